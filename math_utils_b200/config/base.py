@@ -110,13 +110,16 @@ class LayerSpec:
     ``extra``: further parts for an arrangement that wants more than the four
     (a third norm, a gate): ``(name, role, PartSpec)`` each, built like the
     others and handed to the arrangement as ``layer.extra[name]``.  The cache
-    of a layer is its ``mixer``'s; an extra part keeps no cache."""
+    of a layer is its ``mixer``'s; an extra part keeps no cache.
+    ``arrangement_params``: constants of the arrangement itself (a multiplier
+    on what the sublayers add to the stream)."""
     arrangement: str
     norm1: PartSpec
     mixer: PartSpec
     norm2: PartSpec
     feed_forward: PartSpec
     extra: tuple = ()
+    arrangement_params: Mapping[str, Any] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)

@@ -17,6 +17,10 @@
 //                      the head's vdim entries and multiplied by out_scale.  Scores, softmax and sums are
 //                      float32.  Which warp takes which keys depends on the token's position only, so a
 //                      token's result does not depend on the step it ran in.
+//                      Options for other designs: `head_scale` (one float per head that multiplies the head's
+//                      scores besides `scale`), `sink` (the softmax's denominator counts one more key whose score
+//                      is zero and which has no value), `gate` ([T, heads] in the storage type: the head's result
+//                      is multiplied by sigmoid(gate[t][h]), computed in float32).
 #include "common.cuh"
 
 #include <math.h>
@@ -144,7 +148,8 @@ mapped_attention_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
                         const int* __restrict__ block_table, int max_pages, int page_tokens,
                         const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_heads,
                         int n_kv_heads, int dim, int vdim, float scale, int window, float lambda, float out_scale,
-                        float eps, int unit_rms, int vec, TE* __restrict__ out, long long ldo) {
+                        float eps, int unit_rms, int vec, TE* __restrict__ out, long long ldo,
+                        const float* __restrict__ head_scale, int sink, const TE* __restrict__ gate, long long ldg) {
     extern __shared__ float smem[];
     float* qs = smem;                                        // [MAPS][dim]
     float* part_acc = qs + MAPS * dim;                       // [warps][MAPS][vdim]
@@ -155,6 +160,7 @@ mapped_attention_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     const int t = blockIdx.x, h = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = h / (n_heads / n_kv_heads);
     const int pos = tok_pos[t];
+    if (head_scale) scale *= head_scale[h];
     const int* pages = block_table + (long long)tok_seq[t] * max_pages;
     const long long width = (long long)n_kv_heads * (MAPS * dim + vdim);
     const long long key_off = (long long)g * MAPS * dim, val_off = (long long)n_kv_heads * MAPS * dim + (long long)g * vdim;
@@ -230,9 +236,9 @@ mapped_attention_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
         float o[MAPS];
 #pragma unroll
         for (int a = 0; a < MAPS; ++a) {
-            float top = -INFINITY;
+            float top = sink ? 0.0f : -INFINITY;
             for (int w = 0; w < MA_WARPS; ++w) top = fmaxf(top, part_ml[(w * MAPS + a) * 2]);
-            float num = 0.0f, den = 0.0f;
+            float num = 0.0f, den = sink ? expf(-top) : 0.0f;
             for (int w = 0; w < MA_WARPS; ++w) {
                 const float mw = part_ml[(w * MAPS + a) * 2];
                 const float f = mw == -INFINITY ? 0.0f : expf(mw - top);
@@ -247,6 +253,7 @@ mapped_attention_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     }
     float mult = out_scale;
     if (unit_rms) mult *= 1.0f / sqrtf(block_sum(sq, scratch) / (float)vdim + eps);
+    if (gate) mult *= 1.0f / (1.0f + expf(-to_float(gate[(long long)t * ldg + h])));
     __syncthreads();
     for (int d = threadIdx.x; d < vdim; d += blockDim.x)
         out[(long long)t * ldo + (long long)h * vdim + d] = from_float<TE>(part_acc[d] * mult);
@@ -265,7 +272,8 @@ __global__ void __launch_bounds__(128)
 mapped_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restrict__ rows,
                      const int* __restrict__ block_table, int max_pages, const int* __restrict__ tok_pos,
                      const int* __restrict__ tok_seq, int n_heads, int n_kv_heads, int dim, int vdim, float scale,
-                     int window, int vec, float* __restrict__ part_acc, float* __restrict__ part_ml) {
+                     int window, int vec, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                     const float* __restrict__ head_scale) {
     extern __shared__ __align__(16) unsigned char md_raw[];
     const int kw = MAPS * dim, rw = kw + vdim;                 // the kv head's entries of a row
     const int pitch = rw + (vec ? 16 / (int)sizeof(TE) : 1);   // rows start in different banks
@@ -320,6 +328,7 @@ mapped_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restri
         for (int u = 0; u < MD_HEADS; ++u) {
             const int hg = warp + u * warps;                   // the head's place in its group
             if (hg >= group) break;
+            const float scale_h = head_scale ? scale * head_scale[g * group + hg] : scale;
 #pragma unroll
             for (int half = 0; half < MD_KEYS / 32; ++half) {
                 const int jl = half * 32 + lane, j = key0 + jl;
@@ -328,7 +337,7 @@ mapped_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restri
                 float p[MAPS];
 #pragma unroll
                 for (int a = 0; a < MAPS; ++a) {
-                    const float sc = live ? dot_key<TE>(qs + hg * kw + a * dim, tile + jl * pitch + a * dim, dim, vec != 0) * scale
+                    const float sc = live ? dot_key<TE>(qs + hg * kw + a * dim, tile + jl * pitch + a * dim, dim, vec != 0) * scale_h
                                           : -INFINITY;
                     const float m_new = fmaxf(m_run[u][a], warp_max(sc));
                     const float corr = expf(m_run[u][a] - m_new);
@@ -380,7 +389,8 @@ mapped_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restri
 template <typename TE, int MAPS>
 __global__ void __launch_bounds__(128)
 mapped_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int n_heads, int vdim,
-                    float lambda, float out_scale, float eps, int unit_rms, TE* __restrict__ out, long long ldo) {
+                    float lambda, float out_scale, float eps, int unit_rms, TE* __restrict__ out, long long ldo,
+                    int sink, const TE* __restrict__ gate, long long ldg) {
     extern __shared__ float merged[];                        // [vdim]
     __shared__ float scratch[32];
     __shared__ float factor[MAPS][MD_SPLITS];
@@ -390,8 +400,9 @@ mapped_merge_kernel(const float* __restrict__ part_acc, const float* __restrict_
     const long long item0 = ((long long)t * n_heads + h) * MAPS * MD_SPLITS;
     if (threadIdx.x < MAPS) {
         const int a = threadIdx.x;
-        float top = -INFINITY, den = 0.0f;
+        float top = sink ? 0.0f : -INFINITY, den = 0.0f;
         for (int s = 0; s < MD_SPLITS; ++s) top = fmaxf(top, part_ml[(item0 + a * MD_SPLITS + s) * 2]);
+        if (sink) den = expf(-top);
         for (int s = 0; s < MD_SPLITS; ++s) {
             const float m = part_ml[(item0 + a * MD_SPLITS + s) * 2];
             const float f = m == -INFINITY ? 0.0f : expf(m - top);
@@ -417,6 +428,7 @@ mapped_merge_kernel(const float* __restrict__ part_acc, const float* __restrict_
     }
     float mult = out_scale;
     if (unit_rms) mult *= 1.0f / sqrtf(block_sum(sq, scratch) / (float)vdim + eps);
+    if (gate) mult *= 1.0f / (1.0f + expf(-to_float(gate[(long long)t * ldg + h])));
     __syncthreads();
     for (int d = threadIdx.x; d < vdim; d += blockDim.x)
         out[(long long)t * ldo + (long long)h * vdim + d] = from_float<TE>(merged[d] * mult);
@@ -460,7 +472,8 @@ MU_EXPORT int mu_mapped_attention(const void* q, long long ldq, const void* rows
                                   int max_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
                                   int n_tokens, int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale,
                                   int window, float lambda, float out_scale, float eps, int unit_rms, void* out,
-                                  long long ldo, int is_bf16, void* stream) {
+                                  long long ldo, int is_bf16, void* stream, const float* head_scale, int sink,
+                                  const void* gate, long long ldg) {
     if (n_tokens <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || n_heads <= 0 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads || maps < 1 || maps > 2 || dim <= 0 || vdim <= 0 || page_tokens <= 0 || window < 0)
@@ -477,7 +490,8 @@ MU_EXPORT int mu_mapped_attention(const void* q, long long ldq, const void* rows
 #define MU_MAPPED(TE, M)                                                                                              \
     return mu::launch_pdl(mu::mapped_attention_kernel<TE, M>, grid, block, smem, s, 1, (const TE*)q, ldq,             \
                           (const TE*)rows, block_table, max_pages, page_tokens, tok_pos, tok_seq, n_heads, n_kv_heads, \
-                          dim, vdim, scale, window, lambda, out_scale, eps, unit_rms, vec, (TE*)out, ldo)
+                          dim, vdim, scale, window, lambda, out_scale, eps, unit_rms, vec, (TE*)out, ldo, head_scale,  \
+                          sink, (const TE*)gate, ldg)
     if (is_bf16) {
         if (maps == 2) MU_MAPPED(bf, 2);
         MU_MAPPED(bf, 1);
@@ -506,7 +520,8 @@ MU_EXPORT int mu_mapped_attention_decode(const void* q, long long ldq, const voi
                                          int max_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
                                          int n_tokens, int n_heads, int n_kv_heads, int maps, int dim, int vdim,
                                          float scale, int window, float lambda, float out_scale, float eps, int unit_rms,
-                                         float* scratch, void* out, long long ldo, int is_bf16, void* stream) {
+                                         float* scratch, void* out, long long ldo, int is_bf16, void* stream,
+                                         const float* head_scale, int sink, const void* gate, long long ldg) {
     if (n_tokens <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || !scratch || n_heads <= 0 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads || maps < 1 || maps > 2 || dim <= 0 || vdim <= 0 || window < 0)
@@ -533,11 +548,11 @@ MU_EXPORT int mu_mapped_attention_decode(const void* q, long long ldq, const voi
             return MU_ERR_LAUNCH;                                                                                      \
         const int code = mu::launch_pdl(kernel, grid, block, smem, s, 1, (const TE*)q, ldq, (const TE*)rows,           \
                                         block_table, max_pages, tok_pos, tok_seq, n_heads, n_kv_heads, dim, vdim,      \
-                                        scale, window, vec, part_acc, part_ml);                                        \
+                                        scale, window, vec, part_acc, part_ml, head_scale);                            \
         if (code != MU_OK) return code;                                                                                \
         return mu::launch_pdl(mu::mapped_merge_kernel<TE, M>, mgrid, mblock, (size_t)vdim * sizeof(float), s, 1,       \
                               (const float*)part_acc, (const float*)part_ml, n_heads, vdim, lambda, out_scale, eps,    \
-                              unit_rms, (TE*)out, ldo);                                                                \
+                              unit_rms, (TE*)out, ldo, sink, (const TE*)gate, ldg);                                    \
     } while (0)
     if (is_bf16) {
         if (maps == 2) MU_MAPPED_DECODE(bf, 2);

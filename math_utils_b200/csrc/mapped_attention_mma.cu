@@ -4,7 +4,8 @@
 // stages; per map S = Q K^T is mma.sync.m16n8k16 with float32 accumulators, the softmax runs in float32 on the
 // accumulators (running maximum and sum per row), and P V follows with the SAME values for both maps.  The weights
 // P enter that product as two bfloat16 terms (the rounded weight and what the rounding left), so they act with
-// some 16 bits of mantissa instead of 8.  At the end a1 - lambda a2, the head's unit rms and the output scale.
+// some 16 bits of mantissa instead of 8.  At the end a1 - lambda a2, the head's unit rms and the output scale, and
+// the options of mapped_attention.cu (a multiplier per head on the scores, a sink in the denominator, a gate per head).
 //
 // Sizes: page of 64 positions; dim a multiple of 16 up to 256 per map; vdim a multiple of 16 up to 128; the cache
 // row a multiple of 8 entries.  Anything else takes the CUDA-core kernel.
@@ -48,7 +49,9 @@ mapped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, 
                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ tok_pos,
                             const int* __restrict__ tok_seq, const int* __restrict__ tiles, int n_heads, int n_kv_heads,
                             int dim, int vdim, float scale, int window, float lambda, float out_scale, float eps,
-                            int unit_rms, __nv_bfloat16* __restrict__ out, long long ldo) {
+                            int unit_rms, __nv_bfloat16* __restrict__ out, long long ldo,
+                            const float* __restrict__ head_scale, int sink, const __nv_bfloat16* __restrict__ gate,
+                            long long ldg) {
     extern __shared__ __align__(16) unsigned char raw[];
     const int kw = MAPS * dim;                               // key entries of one kv head
     const int kp = kw + MM_PAD, vp = VD + MM_PAD;            // row pitches in shared memory
@@ -61,6 +64,7 @@ mapped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, 
     const int h = blockIdx.y, g = h / (n_heads / n_kv_heads);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gid = lane >> 2, tig = lane & 3;
     const int pos0 = tok_pos[flat0];
+    if (head_scale) scale *= head_scale[h];
     const int* pages = block_table + (long long)tok_seq[flat0] * max_pages;
     const long long width = (long long)n_kv_heads * (kw + vdim);
     const long long key_off = (long long)g * kw, val_off = (long long)n_kv_heads * kw + (long long)g * vdim;
@@ -208,7 +212,14 @@ mapped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, 
             float l = l_run[a][r];
             l += __shfl_xor_sync(0xffffffffu, l, 1);
             l += __shfl_xor_sync(0xffffffffu, l, 2);
-            inv_l[a][r] = l > 0.0f ? 1.0f / l : 0.0f;
+            if (sink) {
+                // one more key of score zero and no value: sums and maximum move to max(m, 0)
+                const float top = fmaxf(m_run[a][r], 0.0f);
+                const float f = m_run[a][r] == -INFINITY ? 0.0f : expf(m_run[a][r] - top);
+                inv_l[a][r] = f / (l * f + expf(-top));
+            } else {
+                inv_l[a][r] = l > 0.0f ? 1.0f / l : 0.0f;
+            }
         }
     float sq[2] = {0.0f, 0.0f};
 #pragma unroll
@@ -229,6 +240,11 @@ mapped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, 
             sq[r] += __shfl_xor_sync(0xffffffffu, sq[r], 2);
             mult[r] *= 1.0f / sqrtf(sq[r] / (float)vdim + eps);
         }
+    }
+    if (gate) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r)
+            if (real[r]) mult[r] *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(long long)(flat0 + row0 + 8 * r) * ldg + h])));
     }
 #pragma unroll
     for (int j = 0; j < VD / 8; ++j) {
@@ -258,7 +274,8 @@ MU_EXPORT int mu_mapped_attention_mma(const void* q, long long ldq, const void* 
                                       int max_pages, int page_tokens, const int* tok_pos, const int* tok_seq,
                                       const int* tiles, int n_tiles, int n_heads, int n_kv_heads, int maps, int dim,
                                       int vdim, float scale, int window, float lambda, float out_scale, float eps,
-                                      int unit_rms, void* out, long long ldo, void* stream) {
+                                      int unit_rms, void* out, long long ldo, void* stream, const float* head_scale,
+                                      int sink, const void* gate, long long ldg) {
     if (n_tiles <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !tiles || !out || n_heads <= 0 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads || window < 0)
@@ -281,7 +298,7 @@ MU_EXPORT int mu_mapped_attention_mma(const void* q, long long ldq, const void* 
             return MU_ERR_LAUNCH;                                                                                      \
         return mu::launch_pdl(kernel, grid, block, smem, s, 1, (const bf*)q, ldq, (const bf*)rows, block_table,        \
                               max_pages, tok_pos, tok_seq, tiles, n_heads, n_kv_heads, dim, vdim, scale, window,       \
-                              lambda, out_scale, eps, unit_rms, (bf*)out, ldo);                                        \
+                              lambda, out_scale, eps, unit_rms, (bf*)out, ldo, head_scale, sink, (const bf*)gate, ldg); \
     } while (0)
     if (maps == 2) {
         if (vd == 32) MU_MAPPED_MMA(2, 32);

@@ -95,19 +95,31 @@ _SIGNATURES = {
     "mu_qk_prepare": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_int, _c_f, _c_int, _c_int, _c_int,
                       _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p],
     "mu_mapped_attention": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                            _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_int, _c_p],
+                            _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_int, _c_p,
+                            _c_p, _c_int, _c_p, _c_ll],
     "mu_mapped_decode_fits": [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int],
     "mu_mapped_decode_scratch": [_c_int, _c_int, _c_int, _c_int],
     "mu_mapped_attention_decode": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                   _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_p],
+                                   _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_p,
+                                   _c_p, _c_int, _c_p, _c_ll],
     "mu_mapped_attention_mma_fits": [_c_int, _c_int, _c_int, _c_int, _c_int],
     "mu_mapped_attention_mma": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
-                                _c_int, _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_p],
+                                _c_int, _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_p,
+                                _c_p, _c_int, _c_p, _c_ll],
+    "mu_qkv_norm_rows": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_f, _c_int, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_p, _c_int, _c_f, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p],
+    "mu_residual_add_norm": [_c_p, _c_ll, _c_p, _c_ll, _c_f, _c_p, _c_f, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p],
+    "mu_delta_prepare": [_c_p, _c_int, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f,
+                         _c_p, _c_p, _c_p, _c_int, _c_p],
+    "mu_delta_scan_max_dk": [],
+    "mu_delta_scan": [_c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll,
+                      _c_ll, _c_p, _c_p],
+    "mu_xielu": [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
     "mu_ssd_conv": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll,
                     _c_int, _c_p, _c_p],
     "mu_ssd_scan": [_c_p, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p,
                     _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_int, _c_p],
-    "mu_gated_group_norm": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_ll, _c_int, _c_p],
+    "mu_gated_group_norm": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_int, _c_int, _c_int, _c_f, _c_p, _c_ll, _c_int, _c_p, _c_int],
     "mu_dynamic_tanh": [_c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p],
     "mu_rms_norm": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_f, _c_p],
     "mu_sigmoid_gate": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
@@ -469,7 +481,9 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
                      n_heads: int, n_kv_heads: int, maps: int, dim: int, vdim: int, scale: float, window: int,
                      out: torch.Tensor, lam: float = 0.0, out_scale: float = 1.0, eps: float = 0.0,
                      unit_rms: bool = False, tiles: Optional[torch.Tensor] = None,
-                     tensor_cores: Optional[bool] = None, single_tokens: bool = False) -> torch.Tensor:
+                     tensor_cores: Optional[bool] = None, single_tokens: bool = False,
+                     head_scale: Optional[torch.Tensor] = None, sink: bool = False,
+                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Softmax attention of every (token, head) over the cached rows it sees (``window`` 0: all up to its own
     position), one result per score map over the same values; with two maps a1 - lam * a2.  ``unit_rms`` brings
     each head's result to unit rms (eps inside the root); ``out_scale`` multiplies it.
@@ -477,8 +491,19 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
     ``tiles`` (int32 [n, 2]: first flat token and count <= 64 of runs of tokens of one sequence, as a prompt step
     has them) sends bfloat16 steps at the sizes ``mu_mapped_attention_mma`` takes to the tensor cores, unless
     ``tensor_cores`` is false.  ``single_tokens`` (every token is the one token of its sequence) takes the kernel
-    that shares a sequence's pages out over blocks and lets the query heads of a kv head read them together."""
-    _need_cuda(q, rows, block_table, tok_pos, tok_seq, out)
+    that shares a sequence's pages out over blocks and lets the query heads of a kv head read them together.
+
+    ``head_scale`` (float32, one per head) multiplies the head's scores besides ``scale``; ``sink`` adds to the
+    softmax's denominator one key of score zero that has no value; ``gate`` ([T, heads] view in the compute dtype)
+    multiplies each head's result by sigmoid(gate[t, h])."""
+    _need_cuda(q, rows, block_table, tok_pos, tok_seq, out, head_scale, gate)
+    if head_scale is not None and (head_scale.dtype != torch.float32 or head_scale.numel() != n_heads
+                                   or not head_scale.is_contiguous()):
+        raise KernelError("mapped_attention: head_scale is one contiguous float32 per head")
+    if gate is not None and (gate.dtype != rows.dtype or gate.dim() != 2 or gate.shape != (q.shape[0], n_heads)
+                             or gate.stride(1) != 1):
+        raise KernelError("mapped_attention: the gate is [T, heads] in the compute dtype with unit inner stride")
+    extras = (_ptr(head_scale), int(sink), _ptr(gate), gate.stride(0) if gate is not None else 0)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
     if (q.dtype != rows.dtype or out.dtype != rows.dtype or q.stride(1) != 1 or out.stride(1) != 1
@@ -495,7 +520,7 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
             _ptr(q), q.stride(0), _ptr(rows), _ptr(block_table), block_table.shape[1], int(page_tokens), _ptr(tok_pos),
             _ptr(tok_seq), q.shape[0], int(n_heads), int(n_kv_heads), int(maps), int(dim), int(vdim), float(scale),
             int(window), float(lam), float(out_scale), float(eps), int(unit_rms), _ptr(room), _ptr(out), out.stride(0),
-            _is_bf16(rows), _stream()),
+            _is_bf16(rows), _stream(), *extras),
             ("mapped_attention_decode(heads={}/{}, maps={}, dim={}, vdim={})", n_heads, n_kv_heads, maps, dim, vdim), launches=2)
         return out
     if tensor_cores is None:
@@ -509,13 +534,13 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
             _ptr(q), q.stride(0), _ptr(rows), _ptr(block_table), block_table.shape[1], int(page_tokens), _ptr(tok_pos),
             _ptr(tok_seq), _ptr(tiles), tiles.shape[0], int(n_heads), int(n_kv_heads), int(maps), int(dim), int(vdim),
             float(scale), int(window), float(lam), float(out_scale), float(eps), int(unit_rms), _ptr(out), out.stride(0),
-            _stream()), ("mapped_attention_mma(heads={}/{}, maps={}, dim={}, vdim={})", n_heads, n_kv_heads, maps, dim, vdim))
+            _stream(), *extras), ("mapped_attention_mma(heads={}/{}, maps={}, dim={}, vdim={})", n_heads, n_kv_heads, maps, dim, vdim))
         return out
     _check(library().mu_mapped_attention(_ptr(q), q.stride(0), _ptr(rows), _ptr(block_table), block_table.shape[1],
                                          int(page_tokens), _ptr(tok_pos), _ptr(tok_seq), q.shape[0], int(n_heads),
                                          int(n_kv_heads), int(maps), int(dim), int(vdim), float(scale), int(window),
                                          float(lam), float(out_scale), float(eps), int(unit_rms), _ptr(out),
-                                         out.stride(0), _is_bf16(rows), _stream()),
+                                         out.stride(0), _is_bf16(rows), _stream(), *extras),
            ("mapped_attention(heads={}/{}, maps={}, dim={}, vdim={})", n_heads, n_kv_heads, maps, dim, vdim))
     return out
 
@@ -563,8 +588,9 @@ def ssd_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias, a_log, skip, n_he
 
 
 def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, parts: int, eps: float,
-                     out: torch.Tensor) -> torch.Tensor:
-    """out = unit_rms_per_part(y * silu(z)) * weight: ``y`` float32, ``z`` and ``out`` in the compute dtype."""
+                     out: torch.Tensor, gate_after: bool = False) -> torch.Tensor:
+    """out = unit_rms_per_part(y * silu(z)) * weight, or with ``gate_after`` unit_rms_per_part(y) * weight * silu(z):
+    ``y`` float32, ``z`` and ``out`` in the compute dtype."""
     _need_cuda(y, z, weight, out)
     inner = y.shape[1]
     if (y.dtype != torch.float32 or y.stride(1) != 1 or z.stride(1) != 1 or out.stride(1) != 1 or z.dtype != out.dtype
@@ -572,8 +598,121 @@ def gated_group_norm(y: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, par
             or inner % parts):
         raise KernelError("gated_group_norm: inputs do not fit")
     _check(library().mu_gated_group_norm(_ptr(y), y.stride(0), _ptr(z), z.stride(0), _ptr(weight), y.shape[0], inner,
-                                         int(parts), float(eps), _ptr(out), out.stride(0), _is_bf16(out), _stream()),
+                                         int(parts), float(eps), _ptr(out), out.stride(0), _is_bf16(out), _stream(),
+                                         int(gate_after)),
            "gated_group_norm")
+    return out
+
+
+# ------------------------------------------------------------------ whole-projection norms, the stream's join
+def qkv_norm_rows(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_weight: torch.Tensor,
+                  k_weight: Optional[torch.Tensor], eps: float, n_kv_heads: int, vdim: int, value_norm: bool, tok_pos,
+                  tok_seq, block_table: Optional[torch.Tensor], page_tokens: int, rows: Optional[torch.Tensor],
+                  first: Optional[torch.Tensor] = None, first_mode: int = 0, mix: float = 0.0) -> None:
+    """Queries [T, q_width] to unit rms over the whole row times ``q_weight``, in place; keys [T, k_width] likewise
+    with ``k_weight`` into the token's cache row, each kv head's values (to unit rms over ``vdim`` with
+    ``value_norm``) behind them.  ``first`` (float32 [T, kv heads * vdim]): ``first_mode`` 1 stores the values
+    there, 2 blends them as (1 - mix) v + mix first before the cache.  ``k`` and ``v`` None: queries only."""
+    _need_cuda(q, k, v, q_weight, k_weight, tok_pos, tok_seq, block_table, rows, first)
+    for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
+        _i32(t, name)
+    if q.dim() != 2 or q.stride(1) != 1 or q_weight.dtype != torch.float32 or q_weight.numel() != q.shape[1]:
+        raise KernelError("qkv_norm_rows: queries are [T, q_width] with unit inner stride and a float32 weight of q_width")
+    k_width = 0
+    if k is not None:
+        k_width = k.shape[1]
+        if (k.dtype != q.dtype or v.dtype != q.dtype or rows.dtype != q.dtype or k.stride(1) != 1 or v.stride(1) != 1
+                or v.shape[1] != n_kv_heads * vdim or not rows.is_contiguous() or rows.shape[1] != page_tokens
+                or rows.shape[2] != k_width + n_kv_heads * vdim or k_weight.dtype != torch.float32
+                or k_weight.numel() != k_width):
+            raise KernelError("qkv_norm_rows: keys, values, weight and cache rows do not fit the sizes given")
+    if first_mode and (first is None or first.dtype != torch.float32 or not first.is_contiguous()
+                       or tuple(first.shape) != (q.shape[0], n_kv_heads * vdim)):
+        raise KernelError("qkv_norm_rows: the shared values are contiguous float32 [T, kv heads * vdim]")
+    _check(library().mu_qkv_norm_rows(_ptr(q), q.stride(0), _ptr(k), k.stride(0) if k is not None else 0, _ptr(v),
+                                      v.stride(0) if v is not None else 0, _ptr(q_weight), _ptr(k_weight), float(eps),
+                                      q.shape[0], q.shape[1], int(k_width), int(n_kv_heads), int(vdim), int(value_norm),
+                                      _ptr(first), int(first_mode), float(mix), _ptr(tok_pos), _ptr(tok_seq),
+                                      _ptr(block_table), block_table.shape[1] if block_table is not None else 0,
+                                      int(page_tokens), _ptr(rows), _is_bf16(q), _stream()),
+           ("qkv_norm_rows(q={}, k={})", q.shape[1], k_width))
+
+
+def residual_add_norm(x: torch.Tensor, y: Optional[torch.Tensor], mult: float, weight: Optional[torch.Tensor],
+                      eps: float, out: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """x += mult * y on the float32 stream (``y`` None: nothing is added), then out = x / rms(x) * weight in
+    ``out``'s dtype (``weight`` None: the addition only)."""
+    _need_cuda(x, y, weight, out)
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("residual_add_norm: the stream is float32 [rows, n] with unit inner stride")
+    if y is not None and (y.dtype != torch.float32 or y.shape != x.shape or y.stride(1) != 1):
+        raise KernelError("residual_add_norm: the sublayer's output is float32 and shaped like the stream")
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != x.shape[1] or not weight.is_contiguous()
+                               or out is None or out.shape != x.shape or out.stride(1) != 1):
+        raise KernelError("residual_add_norm: a float32 weight of n values and an output shaped like the stream")
+    _check(library().mu_residual_add_norm(_ptr(x), x.stride(0), _ptr(y), y.stride(0) if y is not None else 0, float(mult),
+                                          _ptr(weight), float(eps), x.shape[0], x.shape[1], _ptr(out),
+                                          out.stride(0) if out is not None else 0,
+                                          _is_bf16(out) if out is not None else 0, _stream()),
+           ("residual_add_norm(n={})", x.shape[1]))
+    return out
+
+
+def xielu(a: torch.Tensor, pair: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The activation with a quadratic branch above zero and an exponential one below, slopes from ``pair`` (two
+    float32 on the device, each through softplus); ``out`` may be ``a``."""
+    out = a if out is None else out
+    _need_cuda(a, pair, out)
+    if (a.dim() != 2 or a.shape != out.shape or a.dtype != out.dtype or a.stride(1) != 1 or out.stride(1) != 1
+            or pair.dtype != torch.float32 or pair.numel() != 2 or not pair.is_contiguous()):
+        raise KernelError("xielu takes [rows, n] views of one dtype with unit inner stride and two float32 numbers")
+    _check(library().mu_xielu(_ptr(a), a.stride(0), _ptr(pair), _ptr(out), out.stride(0), a.shape[0], a.shape[1],
+                              _is_bf16(a), _stream()), "xielu")
+    return out
+
+
+# ------------------------------------------------------------------ gated delta rule
+def delta_scan_max_dk() -> int:
+    return int(library().mu_delta_scan_max_dk())
+
+
+def delta_prepare(qkv: torch.Tensor, b_raw: torch.Tensor, a_raw: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+                  n_heads: int, n_kv_heads: int, dk: int, q_scale: float, kq: torch.Tensor, beta: torch.Tensor,
+                  decay: torch.Tensor) -> None:
+    """Finishes the convolved rows ``qkv`` (float32 [T, 2 * kv heads * dk + ...]) in place: q and k of every kv head to
+    unit vectors (eps 1e-6 under the root), q times ``q_scale``; ``kq`` [T, kv heads] their product; per head
+    ``beta`` = sigmoid(b_raw) and ``decay`` = exp(-exp(A_log) softplus(a_raw + dt_bias)), float32 [T, heads]."""
+    _need_cuda(qkv, b_raw, a_raw, a_log, dt_bias, kq, beta, decay)
+    T = qkv.shape[0]
+    if (qkv.dtype != torch.float32 or not qkv.is_contiguous() or b_raw.dtype != a_raw.dtype or b_raw.stride(1) != 1
+            or a_raw.stride(1) != 1 or tuple(b_raw.shape) != (T, n_heads) or tuple(a_raw.shape) != (T, n_heads)):
+        raise KernelError("delta_prepare: rows or raw gates do not fit")
+    for t, n in ((a_log, n_heads), (dt_bias, n_heads), (kq, T * n_kv_heads), (beta, T * n_heads), (decay, T * n_heads)):
+        if t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous():
+            raise KernelError("delta_prepare: float32 per-head parameters and outputs of the sizes given")
+    _check(library().mu_delta_prepare(_ptr(qkv), qkv.shape[1], _ptr(b_raw), b_raw.stride(0), _ptr(a_raw), a_raw.stride(0),
+                                      _ptr(a_log), _ptr(dt_bias), T, int(n_heads), int(n_kv_heads), int(dk),
+                                      float(q_scale), _ptr(kq), _ptr(beta), _ptr(decay), _is_bf16(b_raw), _stream()),
+           "delta_prepare")
+
+
+def delta_scan(qkv: torch.Tensor, kq: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, n_heads: int,
+               n_kv_heads: int, dk: int, dv: int, seq_first, seq_slots, state: torch.Tensor, state_offset: int,
+               out: torch.Tensor) -> torch.Tensor:
+    """The recurrence S = decay S; u = beta (v - S^T k); S += k u^T; o = S^T q per (sequence, head) over the step's
+    tokens, from and to ``state[slot][state_offset:]`` (heads x dv x dk float32); ``out`` float32 [T, heads * dv]."""
+    _need_cuda(qkv, kq, beta, decay, seq_first, seq_slots, state, out)
+    _i32(seq_first, "seq_first"); _i32(seq_slots, "seq_slots")
+    T = qkv.shape[0]
+    if (qkv.dtype != torch.float32 or not qkv.is_contiguous() or qkv.shape[1] != 2 * n_kv_heads * dk + n_heads * dv
+            or out.dtype != torch.float32 or not out.is_contiguous() or tuple(out.shape) != (T, n_heads * dv)
+            or state.dtype != torch.float32 or state.stride(1) != 1
+            or state.shape[1] < state_offset + n_heads * dv * dk):
+        raise KernelError("delta_scan: rows, state or output do not fit")
+    _check(library().mu_delta_scan(_ptr(qkv), qkv.shape[1], _ptr(kq), _ptr(beta), _ptr(decay), seq_slots.numel(),
+                                   int(n_heads), int(n_kv_heads), int(dk), int(dv), _ptr(seq_first), _ptr(seq_slots),
+                                   _ptr(state), state.stride(0), int(state_offset), _ptr(out), _stream()),
+           ("delta_scan(heads={}, dk={}, dv={})", n_heads, dk, dv))
     return out
 
 

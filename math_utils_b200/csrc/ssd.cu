@@ -12,7 +12,8 @@
 //               dt = softplus(dt_raw + dt_bias), S = exp(-exp(A_log) dt) S + dt B x^T, y = S^T C + D x;
 //               everything float32; head h reads B and C of group h / (heads / groups).
 // mu_gated_group_norm   y * silu(z), unit rms over each of `parts` equal parts of the row (eps inside the
-//               root), times a weight; output in the compute dtype.
+//               root), times a weight; output in the compute dtype.  With `gate_after` the order is the other
+//               one: y to unit rms per part, times the weight, times silu(z).
 #include "common.cuh"
 
 #include <math.h>
@@ -313,7 +314,8 @@ constexpr int GN_KEEP = 8;       // gated values a thread keeps between the stat
 template <typename TE>
 __global__ void __launch_bounds__(256)
 gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __restrict__ z, long long ldz,
-                        const float* __restrict__ weight, int width, float eps, TE* __restrict__ out, long long ldo) {
+                        const float* __restrict__ weight, int width, float eps, TE* __restrict__ out, long long ldo,
+                        int gate_after) {
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
@@ -325,11 +327,11 @@ gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __
 #pragma unroll
     for (int i = 0; i < GN_KEEP; ++i) {
         const int d = threadIdx.x + i * blockDim.x;
-        kept[i] = d < width ? ys[d] * silu_f(to_float(zs[d])) : 0.0f;
+        kept[i] = d < width ? (gate_after ? ys[d] : ys[d] * silu_f(to_float(zs[d]))) : 0.0f;
         sq += kept[i] * kept[i];
     }
     for (int d = threadIdx.x + GN_KEEP * blockDim.x; d < width; d += blockDim.x) {
-        const float v = ys[d] * silu_f(to_float(zs[d]));
+        const float v = gate_after ? ys[d] : ys[d] * silu_f(to_float(zs[d]));
         sq += v * v;
     }
     const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
@@ -338,7 +340,7 @@ gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __
 #pragma unroll
     for (int i = 0; i < GN_KEEP; ++i) {
         const int d = threadIdx.x + i * blockDim.x;
-        if (d < width) dst[d] = from_float<TE>(kept[i] * inv * w[d]);
+        if (d < width) dst[d] = from_float<TE>(gate_after ? kept[i] * inv * w[d] * silu_f(to_float(zs[d])) : kept[i] * inv * w[d]);
     }
     for (int d = threadIdx.x + GN_KEEP * blockDim.x; d < width; d += blockDim.x)
         dst[d] = from_float<TE>(ys[d] * silu_f(to_float(zs[d])) * inv * w[d]);
@@ -424,7 +426,7 @@ MU_EXPORT int mu_ssd_scan(const float* xbc, int channels, const void* dt_raw, lo
 
 MU_EXPORT int mu_gated_group_norm(const float* y, long long ldy, const void* z, long long ldz, const float* weight,
                                   int n_tokens, int inner, int parts, float eps, void* out, long long ldo, int is_bf16,
-                                  void* stream) {
+                                  void* stream, int gate_after) {
     if (n_tokens <= 0) return MU_OK;
     if (!y || !z || !weight || !out || inner <= 0 || parts <= 0 || inner % parts) return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
@@ -432,7 +434,7 @@ MU_EXPORT int mu_gated_group_norm(const float* y, long long ldy, const void* z, 
     const dim3 grid(n_tokens, parts), block(width >= 1024 ? 256 : 128);
     typedef __nv_bfloat16 bf;
     return is_bf16 ? mu::launch_pdl(mu::gated_group_norm_kernel<bf>, grid, block, 0, s, 1, y, ldy, (const bf*)z, ldz, weight,
-                                    width, eps, (bf*)out, ldo)
+                                    width, eps, (bf*)out, ldo, gate_after)
                    : mu::launch_pdl(mu::gated_group_norm_kernel<float>, grid, block, 0, s, 1, y, ldy, (const float*)z, ldz,
-                                    weight, width, eps, (float*)out, ldo);
+                                    weight, width, eps, (float*)out, ldo, gate_after);
 }

@@ -31,7 +31,7 @@ def build_layer(spec: LayerSpec) -> Layer:
                              "give it a layer of its own in the schedule instead")
         extra[name] = part
     return Layer(
-        arrangement=build_part("arrangement", PartSpec(spec.arrangement)),
+        arrangement=build_part("arrangement", PartSpec(spec.arrangement, dict(getattr(spec, "arrangement_params", {}) or {}))),
         norm1=build_part("norm", spec.norm1),
         mixer=build_part("mixer", spec.mixer),
         norm2=build_part("norm", spec.norm2),

@@ -80,6 +80,7 @@ class StepContext:
     seq_first: Optional[torch.Tensor] = None  # [n_seqs + 1] int32: the flat index of each sequence's first token of the step
     last_tokens: Optional[torch.Tensor] = None  # the cache's [n_slots] int32: the last token each slot was fed
     stream_copy: Optional[torch.Tensor] = None  # the residual stream in the compute dtype, while an arrangement keeps it current
+    pending_join: Optional[tuple] = None    # (stream, sublayer output, multiplier) not added to the stream yet
     trace: Optional[object] = None          # callable(name, tensor): told every named intermediate result
     tag: str = ""                           # prefix of the names noted now ("h.3." inside layer run 3)
 
@@ -92,6 +93,13 @@ class StepContext:
                 # (a trace that only keeps time does not look at values: nothing is computed for it)
                 tensor = tensor.materialize_copy() if getattr(self.trace, "wants_values", True) else None
             self.trace(self.tag + name, tensor)
+
+    def flush_join(self) -> None:
+        """Adds what an arrangement left for the next norm's launch to add (``pending_join``) to the stream now."""
+        if self.pending_join is not None:
+            x, y, mult = self.pending_join
+            self.pending_join = None
+            self.runtime.ops.residual_add_norm(x, y, mult, None, 0.0, None)
 
     @property
     def is_decode(self) -> bool:

@@ -121,6 +121,7 @@ class DecoderModel:
     def forward(self, ctx, cache: SequenceCache) -> Optional[torch.Tensor]:
         a = self.assembly
         ctx.stream_copy = None
+        ctx.pending_join = None
         x = a.embedding.forward(ctx, a.position.embedding_table())
         if a.embedding_norm is not None:
             x = a.embedding_norm.forward_float(x, out=x)
@@ -129,7 +130,10 @@ class DecoderModel:
         for i, entry in enumerate(self.plan.schedule):
             layer = a.layers[entry.layer]
             ctx.tag = f"h.{i}."
+            if ctx.pending_join is not None and not getattr(layer.arrangement, "joins_pending", False):
+                ctx.flush_join()
             layer.arrangement.forward(x, layer, ctx, cache.entry(entry.cache_of), entry.cache_of == i)
+        ctx.flush_join()
         ctx.tag = ""
         if ctx.want_rows is None:
             return None

@@ -15,6 +15,12 @@ kernels.  Every other layer, step and precision goes part by part.
 output norms given as the layer's extra parts ``norm1b`` and ``norm2b``.  A sublayer writes its
 result to a float32 buffer, and the output norm adds its normed rows into the residual stream.  A
 layer without a feed-forward (kind ``none``) stops after the mixer.
+
+``scaled_pre_norm``: x += m * mixer(norm1(x)); x += m * feed_forward(norm2(x)) with one multiplier m
+(parameter ``residual_mult``) on what the sublayers add.  A sublayer writes its result to a float32
+buffer; the addition to the stream is made by the launch of the NEXT norm (``ops.residual_add_norm``:
+x += m * y, then the normed row), also across layers (``StepContext.pending_join``), so the stream is
+read and written once per sublayer.
 """
 from __future__ import annotations
 
@@ -161,5 +167,47 @@ class SandwichNormBlock(Arrangement):
             part.forward(*args)
 
 
+class ScaledPreNormBlock(Arrangement):
+    joins_pending = True             # takes over a join that the layer before left for the next norm
+
+    def __init__(self, spec):
+        super().__init__(spec)
+        self.mult = float(self.param("residual_mult", 1.0))
+
+    def forward(self, x, layer, ctx, cache, owns_cache: bool) -> None:
+        y = ctx.buffer("sublayer.out", tuple(x.shape), torch.float32)
+        h = self._norm(layer.norm1, x, ctx)
+        ctx.note("ln1", h)
+        SandwichNormBlock._sublayer(layer.mixer, y, h, y, ctx, cache, owns_cache)
+        ctx.pending_join = (x, y, self.mult)
+        if ctx.trace is not None:
+            ctx.flush_join()
+            ctx.note("res1", x)
+        if not isinstance(layer.feed_forward, NoFeedForward):
+            h = self._norm(layer.norm2, x, ctx)
+            ctx.note("ln2", h)
+            SandwichNormBlock._sublayer(layer.feed_forward, y, h, y, ctx)
+            ctx.pending_join = (x, y, self.mult)
+        if ctx.trace is not None:
+            ctx.flush_join()
+            ctx.note("res2", x)
+
+    @staticmethod
+    def _norm(norm, x, ctx):
+        """The normed stream, with what is still to be added to the stream added by the same launch."""
+        if isinstance(norm, RmsNorm) and norm.offset == 0.0 and norm.scale == 1.0 and x.stride(1) == 1:
+            pending, ctx.pending_join = ctx.pending_join, None
+            if pending is not None and pending[0] is not x:
+                ctx.pending_join = pending
+                ctx.flush_join()
+                pending = None
+            out = ctx.buffer("stream.normed", tuple(x.shape), norm.runtime.dtype)
+            y, mult = (pending[1], pending[2]) if pending is not None else (None, 0.0)
+            return norm.runtime.ops.residual_add_norm(x, y, mult, norm.weight, norm.eps, out)
+        ctx.flush_join()
+        return norm.forward(x)
+
+
 register_part("arrangement", "pre_norm", PreNormBlock, replace=True)
+register_part("arrangement", "scaled_pre_norm", ScaledPreNormBlock, replace=True)
 register_part("arrangement", "sandwich_norm", SandwichNormBlock, replace=True)
