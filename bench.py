@@ -6,6 +6,7 @@
     python bench.py --only marginal [--batch B]    # each kernel class's share of the recorded decode step
     python bench.py --family forisun [--size s|m] [--batch B] [--steps K]   # Forisun beside GPT-2 at equal size
     python bench.py --family lusalorn [--size s|m] [--batch B] [--steps K]  # Lusalorn beside GPT-2 at equal size
+    python bench.py --family seledra [--size s|m] [--batch B] [--steps K]   # Seledra beside Lusalorn at equal size
 
 A "step" is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (BASELINE.json's third configuration) with seeded random
@@ -514,6 +515,30 @@ def lusalorn_config(size):
     return ours, twin
 
 
+SELEDRA_SIZES = {
+    # width, attention (heads, kv heads, dim, vdim), delta rule (value heads, key heads, dim, vdim, taps), ff, layers
+    "s": (1024, (8, 2, 128, 128), (8, 4, 128, 128, 4), 6144, 4),
+    "m": (2048, (16, 4, 128, 128), (16, 8, 128, 128, 4), 12288, 4),
+}
+
+
+def seledra_config(size):
+    """A Seledra configuration with layer sizes of a real model's order (random weights): an attention layer, two
+    layers of the gated delta rule, an attention layer that blends the first one's values into its own, each with a
+    feed-forward; and beside it the library's closest design, Lusalorn (attention over cached rows, a recurrent
+    mixer with a matrix state), at the same size: equal width, layer count, vocabulary and feed-forward work per
+    token (a gated feed-forward has three matrices where this one has two)."""
+    D, (H, G, d, dv), (dh, dg, dd, dvv, taps), ff, L = SELEDRA_SIZES[size]
+    att = {"heads": H, "kv_heads": G, "dim": d, "vdim": dv, "scale": d ** -0.5, "v_mix": True}
+    rule = {"heads": dh, "kv_heads": dg, "dim": dd, "vdim": dvv, "conv": taps}
+    mlp = {"kind": "dense", "ff": ff}
+    layers = [{"type": "attention" if i in (0, L - 1) else "delta", "mixer": att if i in (0, L - 1) else rule, "mlp": mlp}
+              for i in range(L)]
+    ours = {"architecture": "Seledra", "vocab": FAMILY_VOCAB, "width": D, "max_positions": CONTEXT, "residual_mult": 0.3,
+            "norm": {"eps": 1e-5}, "layers": layers}
+    return ours, lusalorn_config(size)[0]
+
+
 def stage_times(model, prompts, single_steps=8):
     """Device milliseconds per stage of one eager prompt step and of eager single-token steps (their mean)."""
     import torch
@@ -544,10 +569,11 @@ def run_family(args):
     from math_utils_b200.sampling import SamplingParams
     pk = peaks()
     rng = np.random.default_rng(0)
-    configs = forisun_config(args.size) if args.family == "forisun" else lusalorn_config(args.size)
+    configs = {"forisun": forisun_config, "lusalorn": lusalorn_config, "seledra": seledra_config}[args.family](args.size)
+    other = "lusalorn_twin" if args.family == "seledra" else "gpt2_twin"
     record = {"family": args.family, "size": args.size, "batch": args.batch, "steps": args.steps, "dtype": "bfloat16",
               "data": "synthetic: random weights, random tokens", "peaks": pk, "models": {}}
-    for name, cfg in zip((args.family, "gpt2_twin"), configs):
+    for name, cfg in zip((args.family, other), configs):
         llm = load_random(cfg, temperature=0.0, context=CONTEXT)
         model = llm.model
         pre = [rng.integers(0, FAMILY_VOCAB, size=CONTEXT).tolist() for _ in range(PREFILL_SEQS)]
@@ -731,7 +757,7 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="with --only decode: tokens per prompt")
     ap.add_argument("--reference-dir", default="", help="with --impl reference: a checkout other than baseline/_ref")
     ap.add_argument("--tokens", type=int, default=0, help="with --config: fewer tokens per request than fill the context")
-    ap.add_argument("--family", default="", choices=["", "forisun", "lusalorn"],
+    ap.add_argument("--family", default="", choices=["", "forisun", "lusalorn", "seledra"],
                     help="that design at sizes of a real model's order beside GPT-2 at equal size")
     ap.add_argument("--size", default="s", choices=sorted(FORISUN_SIZES), help="with --family: which sizes")
     args = ap.parse_args()

@@ -175,3 +175,66 @@ def forward(config, w, tokens, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.copy())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+# ------------------------------------------------------------------ random weights for tests
+def tensor_shapes(config):
+    D, V = int(config["width"]), int(config["vocab"])
+    shapes = {"embed": (V, D), "pos": (int(config["max_positions"]), D), "final.norm": (D,), "head": (V, D)}
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+        shapes[p + "norm1"] = (D,)
+        x = p + "mix."
+        if layer["type"] == "attention":
+            shapes.update({x + "q": (H * d, D), x + "q.b": (H * d,), x + "k": (G * d, D), x + "k.b": (G * d,),
+                           x + "v": (G * dv, D), x + "v.b": (G * dv,), x + "q.norm": (H * d,), x + "k.norm": (G * d,),
+                           x + "temp": (H,), x + "g": (H, D), x + "o": (D, H * dv)})
+            if m.get("v_mix"):
+                shapes[x + "vmix"] = ()
+        else:
+            taps = int(m["conv"])
+            shapes.update({x + "q": (G * d, D), x + "q.conv": (G * d, taps), x + "k": (G * d, D),
+                           x + "k.conv": (G * d, taps), x + "v": (H * dv, D), x + "v.conv": (H * dv, taps),
+                           x + "b": (H, D), x + "a": (H, D), x + "A_log": (H,), x + "dt_bias": (H,), x + "norm": (dv,),
+                           x + "g": (H * dv, D), x + "o": (D, H * dv)})
+        if layer.get("mlp") is not None:
+            ff = int(layer["mlp"]["ff"])
+            shapes.update({p + "norm2": (D,), p + "mlp.up": (ff, D), p + "mlp.down": (D, ff), p + "mlp.act": (2,)})
+    return shapes
+
+
+def random_weights(config, seed):
+    """Weights that bfloat16 holds exactly (the tests write them to a bfloat16 file), sized so that every mechanism
+    matters: temperatures away from one, a blend well inside (0, 1), decays between nothing and everything."""
+    rng = np.random.default_rng(seed)
+    D = int(config["width"])
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        last = name.rsplit(".", 1)[-1]
+        if name.endswith("norm") or last in ("norm1", "norm2"):
+            a = rng.normal(1.0, 0.2, shape)
+        elif last == "temp":
+            a = rng.uniform(0.5, 2.0, shape)
+        elif last == "vmix":
+            a = rng.uniform(0.25, 0.6, shape)
+        elif last == "conv":
+            a = rng.normal(0.0, 0.6, shape)
+        elif last == "A_log":
+            a = rng.uniform(-2.0, 1.0, shape)
+        elif last == "dt_bias":
+            a = rng.uniform(-3.0, 1.0, shape)
+        elif last == "act":
+            a = rng.normal(0.0, 0.7, shape)
+        elif last == "b" and len(shape) == 1:
+            a = rng.normal(0.0, 0.3, shape)
+        elif name in ("embed", "pos"):
+            a = rng.normal(0.0, 1.0, shape)
+        else:
+            a = rng.normal(0.0, 1.0 / math.sqrt(shape[-1]), shape) * (3.0 if last in ("q", "k", "a", "b") else 1.0)
+        # to what bfloat16 holds: eight bits of mantissa
+        a = np.asarray(a, dtype=np.float32)
+        bits = a.view(np.uint32).astype(np.uint64)
+        bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16
+        out[name] = bits.astype(np.uint32).view(np.float32).astype(F).reshape(shape)
+    return out
