@@ -122,6 +122,8 @@ inline int& pdl_enabled() {
 
 // Launches with the programmatic-serialization attribute (if enabled) and, when cluster_y > 1,
 // as thread-block clusters of (1, cluster_y, 1).
+// launch_after: the same in plain stream order, for a kernel of a few long-running blocks that should find the
+// device empty, so that its blocks are dealt one to an SM and not into the room the kernel before it has left.
 // The kernels of a prompt step ask for the largest shared-memory share of the SM's on-chip memory, whether
 // they use it or not: the large products and the attention need it, and an SM that has to change the split
 // between shared memory and L1 from one kernel to the next first runs empty.  (The kernels of single-token
@@ -136,7 +138,7 @@ inline void prefer_shared_memory(const void* kernel) {
     }
 }
 
-template <typename... KArgs, typename... Args>
+template <bool EARLY = true, typename... KArgs, typename... Args>
 inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                       int cluster_y, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
@@ -146,7 +148,7 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     unsigned n = 0;
-    if (pdl_enabled()) {
+    if (EARLY && pdl_enabled()) {
         attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
@@ -161,6 +163,12 @@ inline int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     cfg.attrs = attr;
     cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? MU_OK : MU_ERR_LAUNCH;
+}
+
+template <typename... KArgs, typename... Args>
+inline int launch_after(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                        Args&&... args) {
+    return launch_pdl<false>(kernel, grid, block, smem, stream, 1, static_cast<Args&&>(args)...);
 }
 
 }  // namespace mu

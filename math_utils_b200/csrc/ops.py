@@ -113,7 +113,7 @@ _SIGNATURES = {
                          _c_p, _c_p, _c_p, _c_int, _c_p],
     "mu_delta_scan_max_dk": [],
     "mu_delta_scan": [_c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_ll,
-                      _c_ll, _c_p, _c_p],
+                      _c_ll, _c_p, _c_int, _c_p],
     "mu_xielu": [_c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
     "mu_ssd_conv": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll,
                     _c_int, _c_p, _c_p],
@@ -711,7 +711,8 @@ def delta_scan(qkv: torch.Tensor, kq: torch.Tensor, beta: torch.Tensor, decay: t
         raise KernelError("delta_scan: rows, state or output do not fit")
     _check(library().mu_delta_scan(_ptr(qkv), qkv.shape[1], _ptr(kq), _ptr(beta), _ptr(decay), seq_slots.numel(),
                                    int(n_heads), int(n_kv_heads), int(dk), int(dv), _ptr(seq_first), _ptr(seq_slots),
-                                   _ptr(state), state.stride(0), int(state_offset), _ptr(out), _stream()),
+                                   _ptr(state), state.stride(0), int(state_offset), _ptr(out),
+                                   int(T > 4 * seq_slots.numel()), _stream()),
            ("delta_scan(heads={}, dk={}, dv={})", n_heads, dk, dv))
     return out
 

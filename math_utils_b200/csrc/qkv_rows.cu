@@ -9,7 +9,8 @@
 //                    Values shared between layers (`first`, float32 [T][kv heads * vdim], rows of this step's tokens):
 //                    mode 1 writes the layer's values there; mode 2 replaces the layer's values by
 //                    (1 - lambda) v + lambda first before they reach the cache.  Statistics, norms and the blend are
-//                    float32; the cache row is rounded once.
+//                    float32; the cache row is rounded once.  Queries, keys and values go to blocks of their own,
+//                    and a block reads its part of the row once.
 // mu_residual_add_norm   x += m * y on the float32 residual stream (y a sublayer's float32 output; y null: nothing is
 //                    added), then h = x / sqrt(mean(x^2) + eps) * w in the compute dtype: the join of one sublayer and
 //                    the input norm of the next in one pass over the row.  With w null only the addition is made.
@@ -19,9 +20,41 @@
 
 namespace mu {
 
+constexpr int QN_KEEP = 8;        // entries of a projection a thread keeps between the sum and the output
+
+// One projection of one token to unit rms over all its entries, times a weight: read once (entries and weights are
+// on their way before the sum is known), kept in registers, written to dst.
+template <typename TE>
+__device__ __forceinline__ void whole_norm_row(const TE* src, const float* __restrict__ weight, int width, float eps,
+                                               TE* dst, float* scratch) {
+    const int tid = threadIdx.x, step = blockDim.x;
+    float kept[QN_KEEP], w[QN_KEEP];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < QN_KEEP; ++i) {
+        const int d = tid + i * step;
+        kept[i] = d < width ? to_float(src[d]) : 0.0f;
+        w[i] = d < width ? weight[d] : 0.0f;
+        ss = fmaf(kept[i], kept[i], ss);
+    }
+    for (int d = tid + QN_KEEP * step; d < width; d += step) {
+        const float x = to_float(src[d]);
+        ss = fmaf(x, x, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    // (src and dst may be the same row: an entry is read and written by the same thread)
+    for (int d = tid + QN_KEEP * step; d < width; d += step) dst[d] = from_float<TE>(to_float(src[d]) * inv * weight[d]);
+#pragma unroll
+    for (int i = 0; i < QN_KEEP; ++i) {
+        const int d = tid + i * step;
+        if (d < width) dst[d] = from_float<TE>(kept[i] * inv * w[i]);
+    }
+}
+
+// blockIdx.y: 0 the queries, 1 the keys, 2 the values; the three do not wait for one another.
 template <typename TE>
 __global__ void __launch_bounds__(128)
-qkv_norm_rows_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k, long long ldk,
+qkv_norm_rows_kernel(TE* q, long long ldq, const TE* __restrict__ k, long long ldk,
                      const TE* __restrict__ v, long long ldv, const float* __restrict__ q_weight,
                      const float* __restrict__ k_weight, float eps, int q_width, int k_width, int n_kv_heads, int vdim,
                      int value_norm, float* __restrict__ first, int first_mode, float lambda,
@@ -30,48 +63,50 @@ qkv_norm_rows_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
-    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
-    {
+    const int t = blockIdx.x, what = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
+    if (what == 0) {
         TE* row = q + (long long)t * ldq;
-        float ss = 0.0f;
-        for (int d = tid; d < q_width; d += blockDim.x) {
-            const float x = to_float(row[d]);
-            ss += x * x;
-        }
-        const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)q_width + eps);
-        for (int d = tid; d < q_width; d += blockDim.x) row[d] = from_float<TE>(to_float(row[d]) * inv * q_weight[d]);
+        whole_norm_row<TE>(row, q_weight, q_width, eps, row, scratch);
+        return;
     }
-    if (!k) return;
     const int pos = tok_pos[t];
     const long long page = block_table[(long long)tok_seq[t] * max_pages + pos / page_tokens];
     TE* dst = rows + (page * page_tokens + pos % page_tokens) * ((long long)k_width + (long long)n_kv_heads * vdim);
-    {
-        const TE* row = k + (long long)t * ldk;
-        float ss = 0.0f;
-        for (int d = tid; d < k_width; d += blockDim.x) {
-            const float x = to_float(row[d]);
-            ss += x * x;
-        }
-        const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)k_width + eps);
-        for (int d = tid; d < k_width; d += blockDim.x) dst[d] = from_float<TE>(to_float(row[d]) * inv * k_weight[d]);
+    if (what == 1) {
+        whole_norm_row<TE>(k + (long long)t * ldk, k_weight, k_width, eps, dst, scratch);
+        return;
     }
     TE* vdst = dst + k_width;
     for (int g = warp; g < n_kv_heads; g += warps) {
         const TE* src = v + (long long)t * ldv + (long long)g * vdim;
-        float inv = 1.0f;
-        if (value_norm) {
-            float ss = 0.0f;
-            for (int d = lane; d < vdim; d += 32) {
-                const float x = to_float(src[d]);
-                ss += x * x;
-            }
-            inv = 1.0f / sqrtf(warp_sum(ss) / (float)vdim + eps);
+        const long long at0 = ((long long)t * n_kv_heads + g) * vdim;
+        float kept[QN_KEEP], other[QN_KEEP];                 // a head's values, and the shared ones they blend with
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < QN_KEEP; ++i) {
+            const int d = lane + 32 * i;
+            kept[i] = d < vdim ? to_float(src[d]) : 0.0f;
+            other[i] = first_mode == 2 && d < vdim ? first[at0 + d] : 0.0f;
+            ss = fmaf(kept[i], kept[i], ss);
         }
-        for (int d = lane; d < vdim; d += 32) {
+        for (int d = lane + 32 * QN_KEEP; d < vdim; d += 32) {
+            const float x = to_float(src[d]);
+            ss = fmaf(x, x, ss);
+        }
+        const float inv = value_norm ? 1.0f / sqrtf(warp_sum(ss) / (float)vdim + eps) : 1.0f;
+#pragma unroll
+        for (int i = 0; i < QN_KEEP; ++i) {
+            const int d = lane + 32 * i;
+            if (d >= vdim) continue;
+            float y = kept[i] * inv;
+            if (first_mode == 1) first[at0 + d] = y;
+            else if (first_mode == 2) y = (1.0f - lambda) * y + lambda * other[i];
+            vdst[(long long)g * vdim + d] = from_float<TE>(y);
+        }
+        for (int d = lane + 32 * QN_KEEP; d < vdim; d += 32) {
             float y = to_float(src[d]) * inv;
-            const long long at = ((long long)t * n_kv_heads + g) * vdim + d;
-            if (first_mode == 1) first[at] = y;
-            else if (first_mode == 2) y = (1.0f - lambda) * y + lambda * first[at];
+            if (first_mode == 1) first[at0 + d] = y;
+            else if (first_mode == 2) y = (1.0f - lambda) * y + lambda * first[at0 + d];
             vdst[(long long)g * vdim + d] = from_float<TE>(y);
         }
     }
@@ -89,12 +124,13 @@ residual_add_norm_kernel(float* __restrict__ x, long long ldx, const float* __re
     const int t = blockIdx.x;
     float* xs = x + (long long)t * ldx;
     const float* ys = y ? y + (long long)t * ldy : nullptr;
-    float kept[RA_KEEP];
+    float kept[RA_KEEP], w[RA_KEEP];
     float sq = 0.0f;
 #pragma unroll
     for (int i = 0; i < RA_KEEP; ++i) {
         const int d = threadIdx.x + i * blockDim.x;
         kept[i] = 0.0f;
+        w[i] = weight && d < width ? weight[d] : 0.0f;        // on its way before the sum is known
         if (d < width) {
             kept[i] = ys ? fmaf(mult, ys[d], xs[d]) : xs[d];
             if (ys) xs[d] = kept[i];
@@ -112,7 +148,7 @@ residual_add_norm_kernel(float* __restrict__ x, long long ldx, const float* __re
 #pragma unroll
     for (int i = 0; i < RA_KEEP; ++i) {
         const int d = threadIdx.x + i * blockDim.x;
-        if (d < width) hs[d] = from_float<TE>(kept[i] * inv * weight[d]);
+        if (d < width) hs[d] = from_float<TE>(kept[i] * inv * w[i]);
     }
     for (int d = threadIdx.x + RA_KEEP * blockDim.x; d < width; d += blockDim.x)
         hs[d] = from_float<TE>(xs[d] * inv * weight[d]);      // written by this very thread above
@@ -134,7 +170,7 @@ MU_EXPORT int mu_qkv_norm_rows(void* q, long long ldq, const void* k, long long 
               n_kv_heads <= 0 || vdim <= 0))
         return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(n_tokens), block(128);
+    const dim3 grid(n_tokens, k ? 3 : 1), block(128);
     typedef __nv_bfloat16 bf;
     if (is_bf16)
         return mu::launch_pdl(mu::qkv_norm_rows_kernel<bf>, grid, block, 0, s, 1, (bf*)q, ldq, (const bf*)k, ldk,

@@ -346,6 +346,43 @@ gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __
         dst[d] = from_float<TE>(ys[d] * silu_f(to_float(zs[d])) * inv * w[d]);
 }
 
+// The same for parts of up to 32 * GN_KEEP entries (a head's values, as a rule): a warp a part, four parts a block,
+// no barrier; the gate and the weight are on their way before the statistics are known.
+template <typename TE>
+__global__ void __launch_bounds__(128)
+gated_group_norm_warp_kernel(const float* __restrict__ y, long long ldy, const TE* __restrict__ z, long long ldz,
+                             const float* __restrict__ weight, int width, int parts, long long n_parts, float eps,
+                             TE* __restrict__ out, long long ldo, int gate_after) {
+    pdl_trigger();
+    pdl_wait();
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= n_parts) return;
+    const int lane = threadIdx.x & 31;
+    const long long t = item / parts;
+    const int part = (int)(item % parts);
+    const float* ys = y + t * ldy + (long long)part * width;
+    const TE* zs = z + t * ldz + (long long)part * width;
+    const float* w = weight + (long long)part * width;
+    float kept[GN_KEEP], gate[GN_KEEP], wk[GN_KEEP];
+    float sq = 0.0f;
+#pragma unroll
+    for (int i = 0; i < GN_KEEP; ++i) {
+        const int d = lane + 32 * i;
+        const bool in = d < width;
+        gate[i] = in ? silu_f(to_float(zs[d])) : 0.0f;
+        wk[i] = in ? w[d] : 0.0f;
+        kept[i] = in ? (gate_after ? ys[d] : ys[d] * gate[i]) : 0.0f;
+        sq = fmaf(kept[i], kept[i], sq);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    TE* dst = out + t * ldo + (long long)part * width;
+#pragma unroll
+    for (int i = 0; i < GN_KEEP; ++i) {
+        const int d = lane + 32 * i;
+        if (d < width) dst[d] = from_float<TE>(gate_after ? kept[i] * inv * wk[i] * gate[i] : kept[i] * inv * wk[i]);
+    }
+}
+
 }  // namespace mu
 
 // u: the convolution's input channels of the step's tokens ([T, channels] view of the projection, compute dtype).
@@ -431,8 +468,17 @@ MU_EXPORT int mu_gated_group_norm(const float* y, long long ldy, const void* z, 
     if (!y || !z || !weight || !out || inner <= 0 || parts <= 0 || inner % parts) return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const int width = inner / parts;
-    const dim3 grid(n_tokens, parts), block(width >= 1024 ? 256 : 128);
     typedef __nv_bfloat16 bf;
+    if (width <= 32 * mu::GN_KEEP && parts > 1) {
+        const long long n_parts = (long long)n_tokens * parts;
+        const dim3 grid((unsigned)((n_parts + 3) / 4)), block(128);
+        return is_bf16 ? mu::launch_pdl(mu::gated_group_norm_warp_kernel<bf>, grid, block, 0, s, 1, y, ldy, (const bf*)z,
+                                        ldz, weight, width, parts, n_parts, eps, (bf*)out, ldo, gate_after)
+                       : mu::launch_pdl(mu::gated_group_norm_warp_kernel<float>, grid, block, 0, s, 1, y, ldy,
+                                        (const float*)z, ldz, weight, width, parts, n_parts, eps, (float*)out, ldo,
+                                        gate_after);
+    }
+    const dim3 grid(n_tokens, parts), block(width >= 1024 ? 256 : 128);
     return is_bf16 ? mu::launch_pdl(mu::gated_group_norm_kernel<bf>, grid, block, 0, s, 1, y, ldy, (const bf*)z, ldz, weight,
                                     width, eps, (bf*)out, ldo, gate_after)
                    : mu::launch_pdl(mu::gated_group_norm_kernel<float>, grid, block, 0, s, 1, y, ldy, (const float*)z, ldz,
