@@ -124,13 +124,12 @@ residual_add_norm_kernel(float* __restrict__ x, long long ldx, const float* __re
     const int t = blockIdx.x;
     float* xs = x + (long long)t * ldx;
     const float* ys = y ? y + (long long)t * ldy : nullptr;
-    float kept[RA_KEEP], w[RA_KEEP];
+    float kept[RA_KEEP];
     float sq = 0.0f;
 #pragma unroll
     for (int i = 0; i < RA_KEEP; ++i) {
         const int d = threadIdx.x + i * blockDim.x;
         kept[i] = 0.0f;
-        w[i] = weight && d < width ? weight[d] : 0.0f;        // on its way before the sum is known
         if (d < width) {
             kept[i] = ys ? fmaf(mult, ys[d], xs[d]) : xs[d];
             if (ys) xs[d] = kept[i];
@@ -148,7 +147,7 @@ residual_add_norm_kernel(float* __restrict__ x, long long ldx, const float* __re
 #pragma unroll
     for (int i = 0; i < RA_KEEP; ++i) {
         const int d = threadIdx.x + i * blockDim.x;
-        if (d < width) hs[d] = from_float<TE>(kept[i] * inv * w[i]);
+        if (d < width) hs[d] = from_float<TE>(kept[i] * inv * weight[d]);
     }
     for (int d = threadIdx.x + RA_KEEP * blockDim.x; d < width; d += blockDim.x)
         hs[d] = from_float<TE>(xs[d] * inv * weight[d]);      // written by this very thread above

@@ -346,8 +346,8 @@ gated_group_norm_kernel(const float* __restrict__ y, long long ldy, const TE* __
         dst[d] = from_float<TE>(ys[d] * silu_f(to_float(zs[d])) * inv * w[d]);
 }
 
-// The same for parts of up to 32 * GN_KEEP entries (a head's values, as a rule): a warp a part, four parts a block,
-// no barrier; the gate and the weight are on their way before the statistics are known.
+// The same for parts of up to 32 * GN_KEEP entries (a head's values, as a rule): a warp a part, one or four parts a
+// block, no barrier; the gate and the weight are on their way before the statistics are known.
 template <typename TE>
 __global__ void __launch_bounds__(128)
 gated_group_norm_warp_kernel(const float* __restrict__ y, long long ldy, const TE* __restrict__ z, long long ldz,
@@ -471,7 +471,8 @@ MU_EXPORT int mu_gated_group_norm(const float* y, long long ldy, const void* z, 
     typedef __nv_bfloat16 bf;
     if (width <= 32 * mu::GN_KEEP && parts > 1) {
         const long long n_parts = (long long)n_tokens * parts;
-        const dim3 grid((unsigned)((n_parts + 3) / 4)), block(128);
+        const int warps = n_parts >= 4096 ? 4 : 1;            // a few parts: a block each, spread over the SMs
+        const dim3 grid((unsigned)((n_parts + warps - 1) / warps)), block(32 * warps);
         return is_bf16 ? mu::launch_pdl(mu::gated_group_norm_warp_kernel<bf>, grid, block, 0, s, 1, y, ldy, (const bf*)z,
                                         ldz, weight, width, parts, n_parts, eps, (bf*)out, ldo, gate_after)
                        : mu::launch_pdl(mu::gated_group_norm_warp_kernel<float>, grid, block, 0, s, 1, y, ldy,

@@ -294,8 +294,25 @@ def test_activation_kernel():
                 assert np.abs(out - want).max() < tol * max(1.0, np.abs(want).max())
 
 
+def test_activation_of_bfloat16_rows_is_as_good_as_their_rounding():
+    """The form for bfloat16 rows (a series near zero, the fast exponential beyond) against the exact one, entry by
+    entry and relative to the entry: tiny and large arguments, and both sides of where the form changes."""
+    ops = _ops()
+    neg = -np.logspace(-6, 2, 440)
+    z = np.concatenate([neg, np.logspace(-6, 2, 120), [-0.25, -0.2500001, -0.2499999, -0.26, -0.24, 0.0, -87.0, -120.0]])
+    z = np.concatenate([z, np.zeros(-len(z) % 64)]).reshape(-1, 64)
+    for pair in ((0.3, -0.4), (-2.0, 1.5), (3.0, 4.0)):
+        zd = dev(z, torch.bfloat16)
+        zf = zd.float().cpu().numpy().astype(np.float64)
+        out = ops.xielu(zd, dev(np.array(pair))).float().cpu().numpy().astype(np.float64)
+        want = plain.xielu(zf, np.array(pair))
+        assert np.all(np.abs(out - want) <= 2.0 ** -7 * np.abs(want) + 1e-9)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,G,dim,vdim,mode", [(4, 2, 16, 24, 1), (3, 3, 6, 5, 2), (6, 1, 5, 15, 0), (8, 2, 32, 64, 2)])
+# the last two: queries wider than the entries a block keeps in registers, values longer than a warp keeps
+@pytest.mark.parametrize("H,G,dim,vdim,mode", [(4, 2, 16, 24, 1), (3, 3, 6, 5, 2), (6, 1, 5, 15, 0), (8, 2, 32, 64, 2),
+                                               (10, 10, 128, 8, 1), (2, 1, 8, 300, 2)])
 def test_projection_norms_and_shared_values_kernel(dtype, H, G, dim, vdim, mode):
     """Queries and keys normed over the whole projection, values per head, the blend with another layer's values,
     rows written to scattered pages."""
@@ -472,7 +489,7 @@ def test_attention_with_sink_on_tensor_cores_prompt_tiles(H, G, dim, vdim):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,dk,dv,taps", [(4, 2, 16, 8, 4), (3, 3, 7, 5, 2), (2, 1, 33, 9, 1), (2, 2, 128, 64, 3),
-                                            (2, 1, 200, 20, 2), (4, 4, 64, 17, 4)])
+                                            (2, 1, 200, 20, 2), (4, 4, 64, 17, 4), (2, 2, 16, 300, 2)])
 def test_delta_rule_kernels(dtype, H, G, dk, dv, taps):
     """Convolution, preparation, recurrence and gated norm against the plain mixer with identity matrices around them:
     a prompt cut into steps of several sizes for two sequences that share the steps."""
