@@ -562,8 +562,8 @@ def stage_times(model, prompts, single_steps=8):
 
 
 def run_family(args):
-    """``--family forisun | lusalorn``: prompt and single-token throughput of that design at sizes of a real model's order beside
-    GPT-2 at equal size, the same workload shape as the default run (2 x 1,024-token prompts; a batch from
+    """``--family forisun | lusalorn | seledra``: prompt and single-token throughput of that design at sizes of a real
+    model's order beside GPT-2 (Seledra: beside Lusalorn) at equal size, the same workload shape as the default run (2 x 1,024-token prompts; a batch from
     512-token prompts towards 1,024).  Prints one JSON line; the default run and its line are not touched."""
     import numpy as np
     from math_utils_b200.sampling import SamplingParams
@@ -758,7 +758,7 @@ def main():
     ap.add_argument("--reference-dir", default="", help="with --impl reference: a checkout other than baseline/_ref")
     ap.add_argument("--tokens", type=int, default=0, help="with --config: fewer tokens per request than fill the context")
     ap.add_argument("--family", default="", choices=["", "forisun", "lusalorn", "seledra"],
-                    help="that design at sizes of a real model's order beside GPT-2 at equal size")
+                    help="that design at sizes of a real model's order beside GPT-2 (seledra: beside Lusalorn) at equal size")
     ap.add_argument("--size", default="s", choices=sorted(FORISUN_SIZES), help="with --family: which sizes")
     args = ap.parse_args()
     if args.gpus != 1:

@@ -246,6 +246,49 @@ def test_conversation_on_a_kept_slot(folders):
         seq.append(tok)
 
 
+@pytest.mark.parametrize("name,dtype", [("a", "float32"), ("b", "bfloat16")])
+def test_replay_of_steps_through_the_program(folders, name, dtype, tmp_path):
+    """``bin/trace_run``: a batch of unequal prompts decoded together, requests that end early, then a second batch
+    that takes over the freed slots, pages and states; every position's logits against the plain model."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lens = {"p": 97, "q": 12, "r": 70, "s": 3, "t": 131}
+    reqs = {rid: tokens_for(name, n, seed=70 + i) for i, (rid, n) in enumerate(lens.items())}
+    steps, rows = [], {rid: [] for rid in reqs}                   # rows[rid]: (step, index in the step's file) per position
+    for ids, cuts in ((("p", "q", "r"), (64, 10, 1)), (("s", "t"), (2, 129))):
+        pos = dict(zip(ids, cuts))
+        entries = [{"id": i, "tokens": reqs[i][:pos[i]], "want": list(range(pos[i]))} for i in ids]
+        live = list(ids)
+        while live:
+            step, at = len(steps), 0
+            for e in entries:
+                rows[e["id"]] += [(step, at + k) for k in e["want"]]
+                at += len(e["want"])
+            ends = [i for i in live if pos[i] >= lens[i]]
+            steps.append({"step": step, "entries": entries, "end": ends})
+            live = [i for i in live if i not in ends]
+            entries = [{"id": i, "tokens": [reqs[i][pos[i]]], "want": [0]} for i in live]
+            for i in live:
+                pos[i] += 1
+    out_dir = str(tmp_path / "out")
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folders[name], "--dtype", dtype,
+                           "--out", out_dir, "--max-tokens", "320"],
+                          input="".join(json.dumps(st) + "\n" for st in steps), capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-3000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == [f"done {st['step']}" for st in steps]
+    vocab = CONFIGS[name]["vocab"]
+    files = {}
+    for rid, r in reqs.items():
+        got = []
+        for step, k in rows[rid]:
+            if step not in files:
+                files[step] = np.fromfile(os.path.join(out_dir, f"{step}.f32"), dtype="<f4").reshape(-1, vocab)
+            got.append(files[step][k])
+        assert len(got) == lens[rid]
+        check_logits(np.stack(got), plain_logits(name, r), dtype, f"seledra {name} replayed request {rid}")
+
+
 # ------------------------------------------------------------------ mechanisms alone
 def _ops():
     from math_utils_b200.csrc import ops
