@@ -33,6 +33,7 @@ constexpr int ACT_NONE = 0;
 constexpr int ACT_GELU_NEW = 1;   // tanh form
 constexpr int ACT_GELU_ERF = 2;   // exact form
 constexpr int ACT_SILU = 3;       // z * sigmoid(z): for the gated feed-forward's own kernel
+constexpr int ACT_RELU2 = 4;      // max(z, 0)^2
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -59,14 +60,20 @@ __device__ __forceinline__ float gelu_new_fast(float x) {
     return __fdividef(x, 1.0f + __expf(-2.0f * y));
 }
 // The activation for an output that is stored as bfloat16.
+__device__ __forceinline__ float relu2(float x) {
+    const float r = fmaxf(x, 0.0f);
+    return r * r;
+}
 __device__ __forceinline__ float apply_act_bf16(float x, int act) {
     if (act == ACT_GELU_NEW) return gelu_new_fast(x);
     if (act == ACT_GELU_ERF) return gelu_erf(x);
+    if (act == ACT_RELU2) return relu2(x);
     return x;
 }
 __device__ __forceinline__ float apply_act(float x, int act) {
     if (act == ACT_GELU_NEW) return gelu_new(x);
     if (act == ACT_GELU_ERF) return gelu_erf(x);
+    if (act == ACT_RELU2) return relu2(x);
     return x;
 }
 

@@ -65,6 +65,7 @@ __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.w
 __device__ __forceinline__ float gr_act(float x, int act, bool to_bf16) {
     if (act == ACT_GELU_NEW) return to_bf16 ? gelu_new_fast(x) : gelu_new(x);
     if (act == ACT_GELU_ERF) return gelu_erf(x);
+    if (act == ACT_RELU2) return relu2(x);
     return x;
 }
 

@@ -39,6 +39,7 @@ constexpr int TC_PATCH_PITCH = 33;               // floats per row of an epilogu
 template <int ACT> __device__ __forceinline__ float tc_act(float x, bool to_bf16) {
     if (ACT == ACT_GELU_NEW) return to_bf16 ? gelu_new_fast(x) : gelu_new(x);
     if (ACT == ACT_GELU_ERF) return gelu_erf(x);
+    if (ACT == ACT_RELU2) return relu2(x);
     return x;
 }
 
@@ -454,6 +455,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     else if (act == ACT_GELU_ERF)
                         tc_finish_split<ACT_GELU_ERF, TC, BN>(ws_tile, splits, who, TC_EPI_WARPS * 32, bias, residual, C, N,
                                                               m0, n0, rows, ldc, ldr);
+                    else if (act == ACT_RELU2)
+                        tc_finish_split<ACT_RELU2, TC, BN>(ws_tile, splits, who, TC_EPI_WARPS * 32, bias, residual, C, N,
+                                                           m0, n0, rows, ldc, ldr);
                     else
                         tc_finish_split<0, TC, BN>(ws_tile, splits, who, TC_EPI_WARPS * 32, bias, residual, C, N, m0, n0,
                                                    rows, ldc, ldr);
@@ -477,6 +481,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         tc_finish_block_bulk<ACT_GELU_NEW, TC>(r, patch, lane, bias, &map_c, N, row0, nb, bulk_out == 2);
                     else if (act == ACT_GELU_ERF)
                         tc_finish_block_bulk<ACT_GELU_ERF, TC>(r, patch, lane, bias, &map_c, N, row0, nb, bulk_out == 2);
+                    else if (act == ACT_RELU2)
+                        tc_finish_block_bulk<ACT_RELU2, TC>(r, patch, lane, bias, &map_c, N, row0, nb, bulk_out == 2);
                     else
                         tc_finish_block_bulk<0, TC>(r, patch, lane, bias, &map_c, N, row0, nb, bulk_out == 2);
                     continue;
@@ -489,6 +495,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 else if (act == ACT_GELU_ERF)
                     tc_finish_block<ACT_GELU_ERF, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N,
                                                       row0, nb, ldc, ldr, vec_ok && nb + 32 <= N);
+                else if (act == ACT_RELU2)
+                    tc_finish_block<ACT_RELU2, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N,
+                                                   row0, nb, ldc, ldr, vec_ok && nb + 32 <= N);
                 else
                     tc_finish_block<0, TC>(r, patch, lane, bias, bias_col[q], residual, C, M, N, row0, nb,
                                            ldc, ldr, vec_ok && nb + 32 <= N);

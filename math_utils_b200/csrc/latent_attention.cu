@@ -18,6 +18,9 @@
 //                    the keys), a warp per key, each lane holding its share of the row in registers so that
 //                    the row is read once for the score and the sum; float32 throughout; partial results
 //                    of splits are merged by a second kernel in split order.
+//                    Options for other designs: `pairs` (mu_latent_append: entry 2i turns with entry 2i + 1
+//                    instead of entry i with entry i + dims/2) and `sink` (one float per head: the softmax's
+//                    denominator also counts exp(sink[h]), unscaled and with no value behind it).
 #include "common.cuh"
 
 #include <math.h>
@@ -61,7 +64,8 @@ __global__ void latent_append_kernel(const T* __restrict__ dkv, long long ld, co
                                      const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
                                      const int* __restrict__ block_table, int max_pages, int page_tokens,
                                      T* __restrict__ rows, const T* __restrict__ q, long long ldq, int q_head_stride,
-                                     float* __restrict__ qa, long long ldqa, int qa_head_stride, int n_heads) {
+                                     float* __restrict__ qa, long long ldqa, int qa_head_stride, int n_heads,
+                                     int pairs) {
     __shared__ float scratch[32];
     pdl_trigger();
     pdl_wait();
@@ -80,9 +84,10 @@ __global__ void latent_append_kernel(const T* __restrict__ dkv, long long ld, co
                 float sn, cs;
                 sincosf(pos * freqs[e], &sn, &cs);
                 sn *= mag; cs *= mag;
-                const float u = to_float(s[e]), v = to_float(s[e + half]);
-                d[e] = u * cs - v * sn;
-                d[e + half] = v * cs + u * sn;
+                const int lo = pairs ? 2 * e : e, hi = pairs ? 2 * e + 1 : e + half;
+                const float u = to_float(s[lo]), v = to_float(s[hi]);
+                d[lo] = u * cs - v * sn;
+                d[hi] = v * cs + u * sn;
             } else {
                 d[e + half] = to_float(s[e + half]);
             }
@@ -109,9 +114,10 @@ __global__ void latent_append_kernel(const T* __restrict__ dkv, long long ld, co
             float sn, cs;
             sincosf(pos * freqs[e], &sn, &cs);
             sn *= mag; cs *= mag;
-            const float u = to_float(src[e]), v = to_float(src[e + half]);
-            dst[e] = from_float<T>(u * cs - v * sn);
-            dst[e + half] = from_float<T>(v * cs + u * sn);
+            const int lo = pairs ? 2 * e : e, hi = pairs ? 2 * e + 1 : e + half;
+            const float u = to_float(src[lo]), v = to_float(src[hi]);
+            dst[lo] = from_float<T>(u * cs - v * sn);
+            dst[hi] = from_float<T>(v * cs + u * sn);
         } else {
             dst[e + half] = src[e + half];
         }
@@ -126,7 +132,8 @@ __global__ void __launch_bounds__(LA_WARPS * 32)
 latent_attention_kernel(const float* __restrict__ q, const T* __restrict__ rows, const int* __restrict__ block_table,
                         int max_pages, int page_tokens, const int* __restrict__ tok_pos,
                         const int* __restrict__ tok_seq, int n_heads, int kv_rank, int width, float scale, int n_splits,
-                        T* __restrict__ out, long long ldo, float* __restrict__ part_o, float* __restrict__ part_ml) {
+                        T* __restrict__ out, long long ldo, float* __restrict__ part_o, float* __restrict__ part_ml,
+                        const float* __restrict__ sink) {
     __shared__ float sm_m[LA_WARPS], sm_l[LA_WARPS];
     extern __shared__ float sm_acc[];                  // [LA_WARPS][kv_rank]
     pdl_trigger();
@@ -183,7 +190,13 @@ latent_attention_kernel(const float* __restrict__ q, const T* __restrict__ rows,
     }
     if (n_splits == 1) {
         T* dst = out + (long long)t * ldo + (long long)(item % n_heads) * kv_rank;
-        const float inv = 1.0f / sum;
+        float inv = 1.0f / sum;
+        if (sink) {
+            // one more term exp(sink) in the denominator: everything moves to the larger of the two maxima
+            const float sk = sink[item % n_heads], top2 = fmaxf(top, sk);
+            const float g = expf(top - top2);
+            inv = g / (sum * g + expf(sk - top2));
+        }
         for (int d = threadIdx.x; d < kv_rank; d += blockDim.x) {
             float v = 0.0f;
 #pragma unroll
@@ -207,15 +220,16 @@ latent_attention_kernel(const float* __restrict__ q, const T* __restrict__ rows,
 
 template <typename T>
 __global__ void latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_heads,
-                                    int kv_rank, int n_splits, T* __restrict__ out, long long ldo) {
+                                    int kv_rank, int n_splits, T* __restrict__ out, long long ldo,
+                                    const float* __restrict__ sink) {
     pdl_trigger();
     pdl_wait();
     __shared__ float factor[64];                       // the parts' weights, 64 parts at a time
     const int item = blockIdx.x, t = item / n_heads;
     const float* ml = part_ml + (long long)item * n_splits * 2;
-    float top = -INFINITY;
+    float top = sink ? sink[item % n_heads] : -INFINITY;
     for (int s = 0; s < n_splits; ++s) top = fmaxf(top, ml[2 * s]);
-    float sum = 0.0f;
+    float sum = sink ? expf(sink[item % n_heads] - top) : 0.0f;
     for (int s = 0; s < n_splits; ++s) sum += ml[2 * s] == -INFINITY ? 0.0f : ml[2 * s + 1] * expf(ml[2 * s] - top);
     const float inv = 1.0f / sum;
     T* dst = out + (long long)t * ldo + (long long)(item % n_heads) * kv_rank;
@@ -248,22 +262,22 @@ template <typename T, int NPL>
 int launch_latent_attention(const float* q, const T* rows, const int* block_table, int max_pages, int page_tokens,
                             const int* tok_pos, const int* tok_seq, int n_tokens, int n_heads, int kv_rank, int width,
                             float scale, int n_splits, T* out, long long ldo, float* part_o, float* part_ml,
-                            cudaStream_t s) {
+                            const float* sink, cudaStream_t s) {
     const size_t smem = (size_t)LA_WARPS * kv_rank * sizeof(float);
     return launch_pdl(latent_attention_kernel<T, NPL>, dim3(n_tokens * n_heads, n_splits), dim3(LA_WARPS * 32), smem, s, 1,
                       q, rows, block_table, max_pages, page_tokens, tok_pos, tok_seq, n_heads, kv_rank, width, scale,
-                      n_splits, out, ldo, part_o, part_ml);
+                      n_splits, out, ldo, part_o, part_ml, sink);
 }
 
 template <typename T>
 int latent_attention_any(const float* q, const T* rows, const int* block_table, int max_pages, int page_tokens,
                          const int* tok_pos, const int* tok_seq, int n_tokens, int n_heads, int kv_rank, int width,
                          float scale, int n_splits, T* out, long long ldo, float* part_o, float* part_ml,
-                         cudaStream_t s) {
+                         const float* sink, cudaStream_t s) {
 #define MU_LA(N)                                                                                                      \
     if (width <= 32 * N)                                                                                              \
         return launch_latent_attention<T, N>(q, rows, block_table, max_pages, page_tokens, tok_pos, tok_seq, n_tokens, \
-                                             n_heads, kv_rank, width, scale, n_splits, out, ldo, part_o, part_ml, s);
+                                             n_heads, kv_rank, width, scale, n_splits, out, ldo, part_o, part_ml, sink, s);
     MU_LA(2) MU_LA(4) MU_LA(6) MU_LA(8) MU_LA(12) MU_LA(16) MU_LA(20) MU_LA(24) MU_LA(32) MU_LA(48)
 #undef MU_LA
     return MU_ERR_UNSUPPORTED_SIZE;
@@ -294,7 +308,7 @@ MU_EXPORT int mu_latent_append(const void* dkv, long long ld, const float* norm_
                                float mag, int rot_dims, int kv_rank, int rot_dim, const int* tok_pos,
                                const int* tok_seq, const int* block_table, int max_pages, int page_tokens,
                                int n_tokens, void* rows, int is_bf16, const void* q, long long ldq, int q_head_stride,
-                               float* qa, long long ldqa, int qa_head_stride, int n_heads, void* stream) {
+                               float* qa, long long ldqa, int qa_head_stride, int n_heads, void* stream, int pairs) {
     if (n_tokens <= 0) return MU_OK;
     if ((!dkv && !q) || !freqs || !tok_pos || kv_rank <= 0 || rot_dim < 0 || rot_dims % 2 || rot_dims > rot_dim ||
         (dkv && (!norm_w || !tok_seq || !block_table || !rows || page_tokens <= 0)) || (q && (!qa || n_heads <= 0)))
@@ -305,10 +319,10 @@ MU_EXPORT int mu_latent_append(const void* dkv, long long ld, const float* norm_
         return mu::launch_pdl(mu::latent_append_kernel<__nv_bfloat16>, grid, block, 0, s, 1, (const __nv_bfloat16*)dkv,
                               ld, norm_w, eps, freqs, mag, rot_dims, kv_rank, rot_dim, tok_pos, tok_seq, block_table,
                               max_pages, page_tokens, (__nv_bfloat16*)rows, (const __nv_bfloat16*)q, ldq, q_head_stride,
-                              qa, ldqa, qa_head_stride, n_heads);
+                              qa, ldqa, qa_head_stride, n_heads, pairs);
     return mu::launch_pdl(mu::latent_append_kernel<float>, grid, block, 0, s, 1, (const float*)dkv, ld, norm_w, eps,
                           freqs, mag, rot_dims, kv_rank, rot_dim, tok_pos, tok_seq, block_table, max_pages, page_tokens,
-                          (float*)rows, (const float*)q, ldq, q_head_stride, qa, ldqa, qa_head_stride, n_heads);
+                          (float*)rows, (const float*)q, ldq, q_head_stride, qa, ldqa, qa_head_stride, n_heads, pairs);
 }
 
 // q: float32 [n_tokens, n_heads, width]; out: [n_tokens, ldo] with head h at columns h * kv_rank.
@@ -316,7 +330,7 @@ MU_EXPORT int mu_latent_append(const void* dkv, long long ld, const float* norm_
 MU_EXPORT int mu_latent_attention(const float* q, const void* rows, const int* block_table, int max_pages,
                                   int page_tokens, const int* tok_pos, const int* tok_seq, int n_tokens, int n_heads,
                                   int kv_rank, int width, float scale, int n_splits, void* out, long long ldo,
-                                  float* part_o, float* part_ml, int is_bf16, void* stream) {
+                                  float* part_o, float* part_ml, int is_bf16, void* stream, const float* sink) {
     if (n_tokens <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || n_heads <= 0 || kv_rank <= 0 || width < kv_rank ||
         n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (!part_o || !part_ml)))
@@ -327,30 +341,31 @@ MU_EXPORT int mu_latent_attention(const float* q, const void* rows, const int* b
     if (is_bf16)
         code = mu::latent_attention_any<__nv_bfloat16>(q, (const __nv_bfloat16*)rows, block_table, max_pages, page_tokens,
                                                        tok_pos, tok_seq, n_tokens, n_heads, kv_rank, width, scale,
-                                                       n_splits, (__nv_bfloat16*)out, ldo, part_o, part_ml, s);
+                                                       n_splits, (__nv_bfloat16*)out, ldo, part_o, part_ml,
+                                                       n_splits == 1 ? sink : nullptr, s);
     else
         code = mu::latent_attention_any<float>(q, (const float*)rows, block_table, max_pages, page_tokens, tok_pos,
                                                tok_seq, n_tokens, n_heads, kv_rank, width, scale, n_splits, (float*)out,
-                                               ldo, part_o, part_ml, s);
+                                               ldo, part_o, part_ml, n_splits == 1 ? sink : nullptr, s);
     if (code != MU_OK || n_splits == 1) return code;
     const dim3 grid(n_tokens * n_heads), block(kv_rank > 1024 ? 512 : 128);    // a thread keeps up to 8 entries
     if (is_bf16)
         return mu::launch_pdl(mu::latent_merge_kernel<__nv_bfloat16>, grid, block, 0, s, 1, (const float*)part_o,
-                              (const float*)part_ml, n_heads, kv_rank, n_splits, (__nv_bfloat16*)out, ldo);
+                              (const float*)part_ml, n_heads, kv_rank, n_splits, (__nv_bfloat16*)out, ldo, sink);
     return mu::launch_pdl(mu::latent_merge_kernel<float>, grid, block, 0, s, 1, (const float*)part_o,
-                          (const float*)part_ml, n_heads, kv_rank, n_splits, (float*)out, ldo);
+                          (const float*)part_ml, n_heads, kv_rank, n_splits, (float*)out, ldo, sink);
 }
 
 // Merges the partial results of n_splits parts of every (token, head) into out (bfloat16 or float32).
 MU_EXPORT int mu_latent_merge(const float* part_o, const float* part_ml, int n_tokens, int n_heads, int kv_rank,
-                              int n_splits, void* out, long long ldo, int is_bf16, void* stream) {
+                              int n_splits, void* out, long long ldo, int is_bf16, void* stream, const float* sink) {
     if (n_tokens <= 0) return MU_OK;
     if (!part_o || !part_ml || !out || n_heads <= 0 || kv_rank <= 0 || n_splits < 1) return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(n_tokens * n_heads), block(kv_rank > 1024 ? 512 : 128);    // a thread keeps up to 8 entries
     if (is_bf16)
         return mu::launch_pdl(mu::latent_merge_kernel<__nv_bfloat16>, grid, block, 0, s, 1, part_o, part_ml, n_heads,
-                              kv_rank, n_splits, (__nv_bfloat16*)out, ldo);
+                              kv_rank, n_splits, (__nv_bfloat16*)out, ldo, sink);
     return mu::launch_pdl(mu::latent_merge_kernel<float>, grid, block, 0, s, 1, part_o, part_ml, n_heads, kv_rank,
-                          n_splits, (float*)out, ldo);
+                          n_splits, (float*)out, ldo, sink);
 }

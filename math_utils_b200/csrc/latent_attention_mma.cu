@@ -50,7 +50,7 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ tok_pos,
                             const int* __restrict__ tok_seq, const int* __restrict__ tiles, int n_heads, int width,
                             float scale, int n_splits, __nv_bfloat16* __restrict__ out, long long ldo,
-                            float* __restrict__ part_o, float* __restrict__ part_ml) {
+                            float* __restrict__ part_o, float* __restrict__ part_ml, const float* __restrict__ sink) {
     constexpr int KV_RANK = 32 * NT;
     extern __shared__ __align__(16) unsigned char lm_raw[];
     const int w8 = width + 8;                                    // padded row: conflict-free fragment loads
@@ -215,7 +215,18 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
     }
     const int src_a = row_src[ra], src_b = row_src[rb];
     if (n_splits == 1) {
-        const float inv_a = 1.0f / l_a, inv_b = 1.0f / l_b;
+        float inv_a = 1.0f / l_a, inv_b = 1.0f / l_b;
+        if (sink) {
+            // exp(sink[head]) joins the denominator (no value behind it); with splits the merge kernel adds it
+            if (src_a >= 0) {
+                const float sk = sink[src_a % n_heads], top = fmaxf(m_a, sk), f = expf(m_a - top);
+                inv_a = f / (l_a * f + expf(sk - top));
+            }
+            if (src_b >= 0) {
+                const float sk = sink[src_b % n_heads], top = fmaxf(m_b, sk), f = expf(m_b - top);
+                inv_b = f / (l_b * f + expf(sk - top));
+            }
+        }
 #pragma unroll
         for (int i = 0; i < NT; ++i) {
             const int d = g * 8 * NT + i * 8 + 2 * t4;
@@ -250,7 +261,7 @@ inline size_t lm_smem(int width) {
 template <int NT>
 int launch_lm(dim3 grid, size_t smem, cudaStream_t s, const float* q, const __nv_bfloat16* rows, const int* block_table,
               int max_pages, const int* tok_pos, const int* tok_seq, const int* tiles, int n_heads, int width, float scale,
-              int n_splits, __nv_bfloat16* out, long long ldo, float* part_o, float* part_ml) {
+              int n_splits, __nv_bfloat16* out, long long ldo, float* part_o, float* part_ml, const float* sink) {
     static bool set = false;
     if (!set) {
         if (cudaFuncSetAttribute(latent_attention_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
@@ -259,7 +270,8 @@ int launch_lm(dim3 grid, size_t smem, cudaStream_t s, const float* q, const __nv
         set = true;
     }
     return launch_pdl(latent_attention_mma_kernel<NT>, grid, dim3(LM_THREADS), smem, s, 1, q, rows, block_table, max_pages,
-                      tok_pos, tok_seq, tiles, n_heads, width, scale, n_splits, out, ldo, part_o, part_ml);
+                      tok_pos, tok_seq, tiles, n_heads, width, scale, n_splits, out, ldo, part_o, part_ml,
+                      n_splits == 1 ? sink : nullptr);
 }
 
 }  // namespace mu
@@ -273,11 +285,12 @@ MU_EXPORT int mu_latent_attention_mma_fits(int kv_rank, int width, int page_toke
 
 // q float32 [n_tokens][n_heads][width]; out bfloat16 [n_tokens][ldo], head h at columns h * kv_rank.
 // tiles (n_tiles of them) for steps with several tokens a sequence; null: every token is a sequence's one token.
-// With n_splits > 1 the partial results go to part_o / part_ml, for mu_latent_merge.
+// With n_splits > 1 the partial results go to part_o / part_ml, for mu_latent_merge.  sink (one float per head, or
+// null): exp(sink[h]) joins head h's softmax denominator; with splits it is the merge that adds it.
 MU_EXPORT int mu_latent_attention_mma(const float* q, const void* rows, const int* block_table, int max_pages,
                                       const int* tok_pos, const int* tok_seq, const int* tiles, int n_tiles, int n_tokens,
                                       int n_heads, int kv_rank, int width, float scale, int n_splits, void* out,
-                                      long long ldo, float* part_o, float* part_ml, void* stream) {
+                                      long long ldo, float* part_o, float* part_ml, void* stream, const float* sink) {
     if (n_tokens <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || n_heads <= 0 || n_splits < 1 || n_splits > 65535 ||
         (n_splits > 1 && (!part_o || !part_ml || tiles)) || (tiles && n_tiles <= 0) || (ldo & 1))
@@ -293,7 +306,7 @@ MU_EXPORT int mu_latent_attention_mma(const float* q, const void* rows, const in
 #define MU_LM(N)                                                                                                       \
     case N:                                                                                                            \
         return mu::launch_lm<N>(grid, smem, s, q, (const bf*)rows, block_table, max_pages, tok_pos, tok_seq, tiles,    \
-                                n_heads, width, scale, n_splits, (bf*)out, ldo, part_o, part_ml);
+                                n_heads, width, scale, n_splits, (bf*)out, ldo, part_o, part_ml, sink);
     switch (kv_rank / 32) { MU_LM(2) MU_LM(4) MU_LM(8) MU_LM(12) MU_LM(16) }
 #undef MU_LM
     return MU_ERR_UNSUPPORTED_SIZE;

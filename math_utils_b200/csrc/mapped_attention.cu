@@ -11,6 +11,8 @@
 //                      i + rot_dims / 2 by the angle position * freq[i]; cos and sin times a magnitude);
 //                      queries are written back in place, keys and values go to the token's cache row.
 //                      Statistics, angles, cos and sin are float32 whatever the storage type.
+//                      Options for other designs: a null weight leaves the slices as they are (no norm);
+//                      `pairs` rotates entry 2i with entry 2i + 1 instead of entry i with entry i + rot_dims / 2.
 // mu_mapped_attention  per (token, head): softmax attention of each map over the keys the token sees
 //                      (positions max(0, p - window + 1) .. p; window 0: all of 0 .. p), both maps over the
 //                      same values.  With two maps the result is a1 - lambda * a2, brought to unit rms over
@@ -20,7 +22,9 @@
 //                      Options for other designs: `head_scale` (one float per head that multiplies the head's
 //                      scores besides `scale`), `sink` (the softmax's denominator counts one more key whose score
 //                      is zero and which has no value), `gate` ([T, heads] in the storage type: the head's result
-//                      is multiplied by sigmoid(gate[t][h]), computed in float32).
+//                      is multiplied by sigmoid(gate[t][h]), computed in float32), `chunk` (c > 0: a token at
+//                      position p sees the positions p - p % c .. p only, chunks counted from position 0 of the
+//                      sequence; it replaces the window).
 #include "common.cuh"
 
 #include <math.h>
@@ -37,7 +41,8 @@ qk_prepare_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k, l
                   const float* __restrict__ k_weight, const float* __restrict__ freqs, float magnitude,
                   int rot_dims, float eps, int n_heads, int n_kv_heads, int maps, int dim, int vdim,
                   const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
-                  const int* __restrict__ block_table, int max_pages, int page_tokens, TE* __restrict__ rows) {
+                  const int* __restrict__ block_table, int max_pages, int page_tokens, TE* __restrict__ rows,
+                  int pairs) {
     extern __shared__ float staged[];                       // [warps][dim] | cos [rot_dims / 2] | sin [rot_dims / 2]
     pdl_trigger();
     pdl_wait();
@@ -76,17 +81,19 @@ qk_prepare_kernel(TE* __restrict__ q, long long ldq, const TE* __restrict__ k, l
             ss += x * x;
         }
         ss = warp_sum(ss);
-        const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+        const float inv = weight ? 1.0f / sqrtf(ss / (float)dim + eps) : 1.0f;
         __syncwarp();
         for (int d = lane; d < dim; d += 32) {
             float y;
             if (d < rot_dims) {
-                const int i = d < half ? d : d - half;
-                const float a = mine[i] * inv * weight[i], b = mine[i + half] * inv * weight[i + half];
+                // the entry's partner and which of the two it is: (i, i + half) or (2i, 2i + 1)
+                const int i = pairs ? d >> 1 : (d < half ? d : d - half);
+                const int lo = pairs ? 2 * i : i, hi = pairs ? 2 * i + 1 : i + half;
+                const float a = mine[lo] * inv * (weight ? weight[lo] : 1.0f), b = mine[hi] * inv * (weight ? weight[hi] : 1.0f);
                 const float cs = cs_tab[i], sn = sn_tab[i];
-                y = d < half ? a * cs - b * sn : b * cs + a * sn;
+                y = d == lo ? a * cs - b * sn : b * cs + a * sn;
             } else {
-                y = mine[d] * inv * weight[d];
+                y = mine[d] * inv * (weight ? weight[d] : 1.0f);
             }
             dst[d] = from_float<TE>(y);
         }
@@ -149,7 +156,8 @@ mapped_attention_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
                         const int* __restrict__ tok_pos, const int* __restrict__ tok_seq, int n_heads,
                         int n_kv_heads, int dim, int vdim, float scale, int window, float lambda, float out_scale,
                         float eps, int unit_rms, int vec, TE* __restrict__ out, long long ldo,
-                        const float* __restrict__ head_scale, int sink, const TE* __restrict__ gate, long long ldg) {
+                        const float* __restrict__ head_scale, int sink, const TE* __restrict__ gate, long long ldg,
+                        int chunk) {
     extern __shared__ float smem[];
     float* qs = smem;                                        // [MAPS][dim]
     float* part_acc = qs + MAPS * dim;                       // [warps][MAPS][vdim]
@@ -167,7 +175,7 @@ mapped_attention_kernel(const TE* __restrict__ q, long long ldq, const TE* __res
     for (int d = threadIdx.x; d < MAPS * dim; d += blockDim.x)
         qs[d] = to_float(q[(long long)t * ldq + (long long)h * MAPS * dim + d]);
     __syncthreads();
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = chunk > 0 ? pos - pos % chunk : window > 0 ? max(0, pos - window + 1) : 0;
     float m_run[MAPS], l_run[MAPS], acc[MAPS][MA_VPL];
 #pragma unroll
     for (int a = 0; a < MAPS; ++a) {
@@ -273,7 +281,7 @@ mapped_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restri
                      const int* __restrict__ block_table, int max_pages, const int* __restrict__ tok_pos,
                      const int* __restrict__ tok_seq, int n_heads, int n_kv_heads, int dim, int vdim, float scale,
                      int window, int vec, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                     const float* __restrict__ head_scale) {
+                     const float* __restrict__ head_scale, int chunk) {
     extern __shared__ __align__(16) unsigned char md_raw[];
     const int kw = MAPS * dim, rw = kw + vdim;                 // the kv head's entries of a row
     const int pitch = rw + (vec ? 16 / (int)sizeof(TE) : 1);   // rows start in different banks
@@ -285,7 +293,7 @@ mapped_decode_kernel(const TE* __restrict__ q, long long ldq, const TE* __restri
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = blockDim.x >> 5;
     const int group = n_heads / n_kv_heads;
     const int pos = tok_pos[t];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = chunk > 0 ? pos - pos % chunk : window > 0 ? max(0, pos - window + 1) : 0;
     const int page_lo = first / MD_KEYS, page_hi = pos / MD_KEYS;
     const int* pages = block_table + (long long)tok_seq[t] * max_pages;
     const long long width = (long long)n_kv_heads * rw;
@@ -442,12 +450,13 @@ MU_EXPORT int mu_qk_prepare(void* q, long long ldq, const void* k, long long ldk
                             const float* q_weight, const float* k_weight, const float* freqs, float magnitude,
                             int rot_dims, float eps, int n_tokens, int n_heads, int n_kv_heads, int maps, int dim,
                             int vdim, const int* tok_pos, const int* tok_seq, const int* block_table, int max_pages,
-                            int page_tokens, void* rows, int is_bf16, void* stream) {
+                            int page_tokens, void* rows, int is_bf16, void* stream, int pairs) {
     if (n_tokens <= 0) return MU_OK;
-    if (!q || !q_weight || !tok_pos || dim <= 0 || maps < 1 || maps > 2 || rot_dims < 0 || rot_dims % 2 ||
+    if (!q || !tok_pos || dim <= 0 || maps < 1 || maps > 2 || rot_dims < 0 || rot_dims % 2 ||
         rot_dims > dim || (rot_dims > 0 && !freqs) || (k != nullptr) != (v != nullptr))
         return MU_ERR_BAD_ARGUMENT;
-    if (k && (!k_weight || !tok_seq || !block_table || !rows || page_tokens <= 0)) return MU_ERR_BAD_ARGUMENT;
+    if (k && ((k_weight != nullptr) != (q_weight != nullptr) || !tok_seq || !block_table || !rows || page_tokens <= 0))
+        return MU_ERR_BAD_ARGUMENT;
     if (dim > 4096) return MU_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 128;
@@ -461,11 +470,11 @@ MU_EXPORT int mu_qk_prepare(void* q, long long ldq, const void* k, long long ldk
         return mu::launch_pdl(mu::qk_prepare_kernel<bf>, grid, dim3(threads), smem, s, 1, (bf*)q, ldq,
                               (const bf*)k, ldk, (const bf*)v, ldv, q_weight, k_weight, freqs, magnitude, rot_dims, eps,
                               n_heads, n_kv_heads, maps, dim, vdim, tok_pos, tok_seq, block_table, max_pages,
-                              page_tokens, (bf*)rows);
+                              page_tokens, (bf*)rows, pairs);
     return mu::launch_pdl(mu::qk_prepare_kernel<float>, grid, dim3(threads), smem, s, 1, (float*)q, ldq,
                           (const float*)k, ldk, (const float*)v, ldv, q_weight, k_weight, freqs, magnitude, rot_dims,
                           eps, n_heads, n_kv_heads, maps, dim, vdim, tok_pos, tok_seq, block_table, max_pages,
-                          page_tokens, (float*)rows);
+                          page_tokens, (float*)rows, pairs);
 }
 
 MU_EXPORT int mu_mapped_attention(const void* q, long long ldq, const void* rows, const int* block_table,
@@ -473,10 +482,11 @@ MU_EXPORT int mu_mapped_attention(const void* q, long long ldq, const void* rows
                                   int n_tokens, int n_heads, int n_kv_heads, int maps, int dim, int vdim, float scale,
                                   int window, float lambda, float out_scale, float eps, int unit_rms, void* out,
                                   long long ldo, int is_bf16, void* stream, const float* head_scale, int sink,
-                                  const void* gate, long long ldg) {
+                                  const void* gate, long long ldg, int chunk) {
     if (n_tokens <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || n_heads <= 0 || n_kv_heads <= 0 ||
-        n_heads % n_kv_heads || maps < 1 || maps > 2 || dim <= 0 || vdim <= 0 || page_tokens <= 0 || window < 0)
+        n_heads % n_kv_heads || maps < 1 || maps > 2 || dim <= 0 || vdim <= 0 || page_tokens <= 0 || window < 0 ||
+        chunk < 0)
         return MU_ERR_BAD_ARGUMENT;
     if (vdim > 32 * mu::MA_VPL) return MU_ERR_UNSUPPORTED_SIZE;
     const size_t smem = ((size_t)maps * dim + (size_t)mu::MA_WARPS * maps * (vdim + 2)) * sizeof(float);
@@ -491,7 +501,7 @@ MU_EXPORT int mu_mapped_attention(const void* q, long long ldq, const void* rows
     return mu::launch_pdl(mu::mapped_attention_kernel<TE, M>, grid, block, smem, s, 1, (const TE*)q, ldq,             \
                           (const TE*)rows, block_table, max_pages, page_tokens, tok_pos, tok_seq, n_heads, n_kv_heads, \
                           dim, vdim, scale, window, lambda, out_scale, eps, unit_rms, vec, (TE*)out, ldo, head_scale,  \
-                          sink, (const TE*)gate, ldg)
+                          sink, (const TE*)gate, ldg, chunk)
     if (is_bf16) {
         if (maps == 2) MU_MAPPED(bf, 2);
         MU_MAPPED(bf, 1);
@@ -521,10 +531,10 @@ MU_EXPORT int mu_mapped_attention_decode(const void* q, long long ldq, const voi
                                          int n_tokens, int n_heads, int n_kv_heads, int maps, int dim, int vdim,
                                          float scale, int window, float lambda, float out_scale, float eps, int unit_rms,
                                          float* scratch, void* out, long long ldo, int is_bf16, void* stream,
-                                         const float* head_scale, int sink, const void* gate, long long ldg) {
+                                         const float* head_scale, int sink, const void* gate, long long ldg, int chunk) {
     if (n_tokens <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || !scratch || n_heads <= 0 || n_kv_heads <= 0 ||
-        n_heads % n_kv_heads || maps < 1 || maps > 2 || dim <= 0 || vdim <= 0 || window < 0)
+        n_heads % n_kv_heads || maps < 1 || maps > 2 || dim <= 0 || vdim <= 0 || window < 0 || chunk < 0)
         return MU_ERR_BAD_ARGUMENT;
     const int group = n_heads / n_kv_heads;
     if (page_tokens != mu::MD_KEYS || vdim > 32 * mu::MA_VPL || group > 16) return MU_ERR_UNSUPPORTED_SIZE;
@@ -548,7 +558,7 @@ MU_EXPORT int mu_mapped_attention_decode(const void* q, long long ldq, const voi
             return MU_ERR_LAUNCH;                                                                                      \
         const int code = mu::launch_pdl(kernel, grid, block, smem, s, 1, (const TE*)q, ldq, (const TE*)rows,           \
                                         block_table, max_pages, tok_pos, tok_seq, n_heads, n_kv_heads, dim, vdim,      \
-                                        scale, window, vec, part_acc, part_ml, head_scale);                            \
+                                        scale, window, vec, part_acc, part_ml, head_scale, chunk);                     \
         if (code != MU_OK) return code;                                                                                \
         return mu::launch_pdl(mu::mapped_merge_kernel<TE, M>, mgrid, mblock, (size_t)vdim * sizeof(float), s, 1,       \
                               (const float*)part_acc, (const float*)part_ml, n_heads, vdim, lambda, out_scale, eps,    \

@@ -5,7 +5,8 @@
 // accumulators (running maximum and sum per row), and P V follows with the SAME values for both maps.  The weights
 // P enter that product as two bfloat16 terms (the rounded weight and what the rounding left), so they act with
 // some 16 bits of mantissa instead of 8.  At the end a1 - lambda a2, the head's unit rms and the output scale, and
-// the options of mapped_attention.cu (a multiplier per head on the scores, a sink in the denominator, a gate per head).
+// the options of mapped_attention.cu (a multiplier per head on the scores, a sink in the denominator, a gate per head,
+// chunks of positions instead of a window).
 //
 // Sizes: page of 64 positions; dim a multiple of 16 up to 256 per map; vdim a multiple of 16 up to 128; the cache
 // row a multiple of 8 entries.  Anything else takes the CUDA-core kernel.
@@ -51,7 +52,7 @@ mapped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, 
                             int dim, int vdim, float scale, int window, float lambda, float out_scale, float eps,
                             int unit_rms, __nv_bfloat16* __restrict__ out, long long ldo,
                             const float* __restrict__ head_scale, int sink, const __nv_bfloat16* __restrict__ gate,
-                            long long ldg) {
+                            long long ldg, int chunk) {
     extern __shared__ __align__(16) unsigned char raw[];
     const int kw = MAPS * dim;                               // key entries of one kv head
     const int kp = kw + MM_PAD, vp = VD + MM_PAD;            // row pitches in shared memory
@@ -69,7 +70,8 @@ mapped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, 
     const long long width = (long long)n_kv_heads * (kw + vdim);
     const long long key_off = (long long)g * kw, val_off = (long long)n_kv_heads * kw + (long long)g * vdim;
     const int last_key = pos0 + count - 1;
-    const int first_key = window > 0 ? max(0, pos0 - window + 1) : 0;
+    // (with chunks: the first query's chunk starts first; a tile may reach into the next chunk)
+    const int first_key = chunk > 0 ? pos0 - pos0 % chunk : window > 0 ? max(0, pos0 - window + 1) : 0;
     const int page_lo = first_key / MM_TILE, page_hi = last_key / MM_TILE;
 
     // the value columns past vdim stay zero; the queries of the tile (rows past count are zeros)
@@ -124,7 +126,9 @@ mapped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, 
         const int key0 = pg * MM_TILE;
         // a warp whose 16 queries see nothing of this page skips it (a page wholly after them, or wholly before their windows)
         const int w_first = pos0 + warp * 16, w_last = min(pos0 + warp * 16 + 15, last_key);
-        const bool skip = key0 > w_last || (window > 0 && key0 + MM_TILE - 1 < w_first - window + 1) || warp * 16 >= count;
+        const bool skip = key0 > w_last || warp * 16 >= count ||
+                          (chunk > 0 ? key0 + MM_TILE - 1 < w_first - w_first % chunk
+                                     : window > 0 && key0 + MM_TILE - 1 < w_first - window + 1);
         if (!skip) {
 #pragma unroll
             for (int a = 0; a < MAPS; ++a) {
@@ -149,7 +153,8 @@ mapped_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, long long ldq, 
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int r = e >> 1, kj = key0 + j * 8 + tig * 2 + (e & 1);
-                        const bool seen = real[r] && kj <= qpos[r] && (window == 0 || qpos[r] - kj < window);
+                        const bool seen = real[r] && kj <= qpos[r] &&
+                                          (chunk > 0 ? kj >= qpos[r] - qpos[r] % chunk : window == 0 || qpos[r] - kj < window);
                         s[j][e] = seen ? s[j][e] * scale : -INFINITY;
                         top[r] = fmaxf(top[r], s[j][e]);
                     }
@@ -275,10 +280,10 @@ MU_EXPORT int mu_mapped_attention_mma(const void* q, long long ldq, const void* 
                                       const int* tiles, int n_tiles, int n_heads, int n_kv_heads, int maps, int dim,
                                       int vdim, float scale, int window, float lambda, float out_scale, float eps,
                                       int unit_rms, void* out, long long ldo, void* stream, const float* head_scale,
-                                      int sink, const void* gate, long long ldg) {
+                                      int sink, const void* gate, long long ldg, int chunk) {
     if (n_tiles <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !tiles || !out || n_heads <= 0 || n_kv_heads <= 0 ||
-        n_heads % n_kv_heads || window < 0)
+        n_heads % n_kv_heads || window < 0 || chunk < 0)
         return MU_ERR_BAD_ARGUMENT;
     if (!mu_mapped_attention_mma_fits(n_kv_heads, maps, dim, vdim, page_tokens)) return MU_ERR_UNSUPPORTED_SIZE;
     if (((uintptr_t)q & 15) || ((uintptr_t)rows & 15) || ((uintptr_t)out & 3) || ldq % 8 || ldo % 2)
@@ -298,7 +303,8 @@ MU_EXPORT int mu_mapped_attention_mma(const void* q, long long ldq, const void* 
             return MU_ERR_LAUNCH;                                                                                      \
         return mu::launch_pdl(kernel, grid, block, smem, s, 1, (const bf*)q, ldq, (const bf*)rows, block_table,        \
                               max_pages, tok_pos, tok_seq, tiles, n_heads, n_kv_heads, dim, vdim, scale, window,       \
-                              lambda, out_scale, eps, unit_rms, (bf*)out, ldo, head_scale, sink, (const bf*)gate, ldg); \
+                              lambda, out_scale, eps, unit_rms, (bf*)out, ldo, head_scale, sink, (const bf*)gate, ldg, \
+                              chunk);                                                                                  \
     } while (0)
     if (maps == 2) {
         if (vd == 32) MU_MAPPED_MMA(2, 32);

@@ -13,6 +13,13 @@
 //                 tile.  Rows of x are gathered through the slot's pair (token = pair / top) or are the slots
 //                 themselves.
 // mu_moe_combine  y[t, :] = sum over the token's pairs, in the order of its choices, of weight * out[slot, :].
+//
+// Options for other designs.  Identity experts: the router's outputs from `n_real` on have no matrices; their
+// pairs get no slot (slot_of = -1) and no tile, and the combine takes the token's own input row for them.  The
+// router can divide the chosen weights by (their sum + renorm_eps), and compute one more number per token,
+// sigmoid(gate_w . h), which the combine multiplies a shared expert's row by before adding it.  The experts'
+// product takes an activation code (mu::ACT_*) for experts of the form W2 act(W1 x).  The combine can add its
+// result to what `out` holds.
 #include "common.cuh"
 
 #include <math.h>
@@ -30,7 +37,8 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ router,
                  const float* __restrict__ correction, int n_tokens, int hidden, int n_experts, int top,
                  float scale, int softmax, int renormalize, int* __restrict__ expert_of,
-                 float* __restrict__ weight_of) {
+                 float* __restrict__ weight_of, float renorm_eps, const float* __restrict__ gate_w,
+                 float* __restrict__ gate_out) {
     extern __shared__ __align__(16) float sm[];        // row [hidden], scores [n_experts], choice [n_experts]
     pdl_trigger();
     pdl_wait();
@@ -42,9 +50,11 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
     const T* row = h + (long long)t * ldh;
     for (int d = threadIdx.x; d < hidden; d += blockDim.x) hrow[d] = to_float(row[d]);
     __syncthreads();
-    const bool wide = hidden % 4 == 0 && ((uintptr_t)router & 15) == 0;      // rows of the router in 16-byte pieces
-    for (int e = warp; e < n_experts; e += ROUTE_WARPS) {
-        const float* w = router + (long long)e * hidden;
+    const bool wide = hidden % 4 == 0 && ((uintptr_t)router & 15) == 0 &&
+                      ((uintptr_t)gate_w & 15) == 0;                          // rows of the router in 16-byte pieces
+    // (with gate_w: one more sum, over the shared expert's gate row, by the warp whose turn it is)
+    for (int e = warp; e < n_experts + (gate_w ? 1 : 0); e += ROUTE_WARPS) {
+        const float* w = e < n_experts ? router + (long long)e * hidden : gate_w;
         float z = 0.0f;
         if (wide) {
             const float4* w4 = reinterpret_cast<const float4*>(w);
@@ -60,7 +70,10 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
             for (int d = lane; d < hidden; d += 32) z += hrow[d] * w[d];
         }
         z = warp_sum(z);
-        if (lane == 0) score[e] = z;
+        if (lane == 0) {
+            if (e < n_experts) score[e] = z;
+            else gate_out[t] = 1.0f / (1.0f + expf(-z));
+        }
     }
     __syncthreads();
     if (warp != 0) return;
@@ -97,7 +110,7 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
         kept += score[arg];
         __syncwarp();
     }
-    const float f = renormalize ? scale / kept : scale;
+    const float f = renormalize ? scale / (kept + renorm_eps) : scale;
     for (int k = lane; k < top; k += 32) weight_of[(long long)t * top + k] *= f;
 }
 
@@ -105,7 +118,7 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
 // [3 i + 2] = rows; n_tiles[0] = how many.
 __global__ void moe_group_kernel(const int* __restrict__ expert_of, int n_pairs, int n_experts, int* __restrict__ slot_of,
                                  int* __restrict__ pair_of, int* __restrict__ tile_info, int* __restrict__ n_tiles,
-                                 int tile_rows) {
+                                 int tile_rows, int n_real) {
     extern __shared__ int smi[];                       // count [n_experts], first [n_experts + 1], tile0 [n_experts + 1]
     int* count = smi;
     int* first = smi + n_experts;
@@ -114,7 +127,8 @@ __global__ void moe_group_kernel(const int* __restrict__ expert_of, int n_pairs,
     pdl_wait();
     for (int e = threadIdx.x; e < n_experts; e += blockDim.x) count[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) atomicAdd(&count[expert_of[p]], 1);
+    for (int p = threadIdx.x; p < n_pairs; p += blockDim.x)
+        if (expert_of[p] < n_real) atomicAdd(&count[expert_of[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int at = 0, tiles = 0;
@@ -144,6 +158,10 @@ __global__ void moe_group_kernel(const int* __restrict__ expert_of, int n_pairs,
     // itself), so the slots are simply drawn
     for (int p = threadIdx.x; p < n_pairs; p += blockDim.x) {
         const int e = expert_of[p];
+        if (e >= n_real) {                             // an identity expert: nothing to compute
+            slot_of[p] = -1;
+            continue;
+        }
         const int slot = first[e] + atomicAdd(&count[e], 1);
         slot_of[p] = slot;
         pair_of[slot] = p;
@@ -158,7 +176,7 @@ __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ pair_of, int top,
                 const T* __restrict__ w1, const T* __restrict__ w2, long long expert_stride, long long ldw,
                 const int* __restrict__ tile_info, const int* __restrict__ n_tiles, int n, int k,
-                TO* __restrict__ out, long long ldo) {
+                TO* __restrict__ out, long long ldo, int act) {
     __shared__ float sa[MOE_TM][MOE_TK + 1];
     __shared__ float sw1[MOE_TN][MOE_TK + 1];
     __shared__ float sw2[GATED ? MOE_TN : 1][MOE_TK + 1];
@@ -216,22 +234,32 @@ moe_gemm_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ 
         for (int j = 0; j < 4; ++j) {
             const int col = n0 + tx + 16 * j;
             if (col >= n) continue;
-            const float v = GATED ? silu(a1[i][j]) * a2[i][j] : a1[i][j];
+            const float v = GATED ? silu(a1[i][j]) * a2[i][j] : apply_act(a1[i][j], act);
             out[(long long)(slot0 + r) * ldo + col] = from_float<TO>(v);
         }
     }
 }
 
+// x (may be null): the rows the experts read, for pairs without a slot; shared / shared_gate (may be null): a row
+// per token that every token gets, times the token's gate.
+template <typename TX>
 __global__ void moe_combine_kernel(const float* __restrict__ y, long long ldy, const int* __restrict__ slot_of,
                                    const float* __restrict__ weight_of, int top, int width, float* __restrict__ out,
-                                   long long ldo) {
+                                   long long ldo, const TX* __restrict__ x, long long ldx,
+                                   const float* __restrict__ shared, long long lds,
+                                   const float* __restrict__ shared_gate, int add) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
     for (int d = threadIdx.x; d < width; d += blockDim.x) {
         float v = 0.0f;
-        for (int k = 0; k < top; ++k)
-            v += weight_of[(long long)t * top + k] * y[(long long)slot_of[(long long)t * top + k] * ldy + d];
+        for (int k = 0; k < top; ++k) {
+            const int slot = slot_of[(long long)t * top + k];
+            const float row = slot >= 0 ? y[(long long)slot * ldy + d] : to_float(x[(long long)t * ldx + d]);
+            v += weight_of[(long long)t * top + k] * row;
+        }
+        if (shared) v += (shared_gate ? shared_gate[t] : 1.0f) * shared[(long long)t * lds + d];
+        if (add) v += out[(long long)t * ldo + d];
         out[(long long)t * ldo + d] = v;
     }
 }
@@ -268,9 +296,11 @@ MU_EXPORT int mu_moe_tile_rows() { return mu::MOE_TM; }
 
 MU_EXPORT int mu_moe_route(const void* h, long long ldh, int h_bf16, const float* router, const float* correction,
                            int n_tokens, int hidden, int n_experts, int top, float scale, int softmax, int renormalize,
-                           int* expert_of, float* weight_of, void* stream) {
+                           int* expert_of, float* weight_of, void* stream, float renorm_eps, const float* gate_w,
+                           float* gate_out) {
     if (n_tokens <= 0) return MU_OK;
-    if (!h || !router || !expert_of || !weight_of || hidden <= 0 || n_experts <= 0 || top <= 0 || top > n_experts)
+    if (!h || !router || !expert_of || !weight_of || hidden <= 0 || n_experts <= 0 || top <= 0 || top > n_experts ||
+        (gate_w != nullptr) != (gate_out != nullptr))
         return MU_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)(hidden + 2 * n_experts) * sizeof(float);
     if (smem > 48 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
@@ -279,22 +309,25 @@ MU_EXPORT int mu_moe_route(const void* h, long long ldh, int h_bf16, const float
     if (h_bf16)
         return mu::launch_pdl(mu::moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, 1, (const __nv_bfloat16*)h, ldh,
                               router, correction, n_tokens, hidden, n_experts, top, scale, softmax, renormalize,
-                              expert_of, weight_of);
+                              expert_of, weight_of, renorm_eps, gate_w, gate_out);
     return mu::launch_pdl(mu::moe_route_kernel<float>, grid, block, smem, s, 1, (const float*)h, ldh, router, correction,
-                          n_tokens, hidden, n_experts, top, scale, softmax, renormalize, expert_of, weight_of);
+                          n_tokens, hidden, n_experts, top, scale, softmax, renormalize, expert_of, weight_of, renorm_eps,
+                          gate_w, gate_out);
 }
 
 // tile_info needs 3 * (n_pairs / tile_rows + n_experts) ints.  tile_rows: the CUDA-core product takes tiles of
 // mu_moe_tile_rows() slots, the tensor-core product of 32 or 64.
+// n_real (0: all of them): experts from n_real on are identity experts.
 MU_EXPORT int mu_moe_group(const int* expert_of, int n_pairs, int n_experts, int* slot_of, int* pair_of, int* tile_info,
-                           int* n_tiles, int tile_rows, void* stream) {
+                           int* n_tiles, int tile_rows, void* stream, int n_real) {
     if (n_pairs <= 0) return MU_OK;
     if (!expert_of || !slot_of || !pair_of || !tile_info || !n_tiles || n_experts <= 0 || tile_rows <= 0)
         return MU_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)(3 * n_experts + 2) * sizeof(int);
     if (smem > 48 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
+    if (n_real < 0 || n_real > n_experts) return MU_ERR_BAD_ARGUMENT;
     return mu::launch_pdl(mu::moe_group_kernel, dim3(1), dim3(1024), smem, (cudaStream_t)stream, 1, expert_of, n_pairs,
-                          n_experts, slot_of, pair_of, tile_info, n_tiles, tile_rows);
+                          n_experts, slot_of, pair_of, tile_info, n_tiles, tile_rows, n_real > 0 ? n_real : n_experts);
 }
 
 // w1 (and w2 when gated): [n_experts][n][k] with row stride ldw and expert stride `expert_stride` elements.
@@ -302,7 +335,7 @@ MU_EXPORT int mu_moe_group(const int* expert_of, int n_pairs, int n_experts, int
 MU_EXPORT int mu_moe_gemm(const void* x, long long ldx, const int* pair_of, int top, const void* w1, const void* w2,
                           long long expert_stride, long long ldw, const int* tile_info, const int* n_tiles,
                           int max_tiles, int n, int k, void* out, long long ldo, int is_bf16, int out_bf16,
-                          void* stream) {
+                          void* stream, int act) {
     if (max_tiles <= 0) return MU_OK;
     if (!x || !w1 || !tile_info || !n_tiles || !out || n <= 0 || k <= 0 || (pair_of && top <= 0))
         return MU_ERR_BAD_ARGUMENT;
@@ -312,7 +345,7 @@ MU_EXPORT int mu_moe_gemm(const void* x, long long ldx, const int* pair_of, int 
     typedef __nv_bfloat16 bf;
 #define MU_MOE(T, TO, G)                                                                                             \
     return mu::launch_pdl(mu::moe_gemm_kernel<T, TO, G>, grid, block, 0, s, 1, (const T*)x, ldx, pair_of, top,        \
-                          (const T*)w1, (const T*)w2, expert_stride, ldw, tile_info, n_tiles, n, k, (TO*)out, ldo)
+                          (const T*)w1, (const T*)w2, expert_stride, ldw, tile_info, n_tiles, n, k, (TO*)out, ldo, act)
     if (w2) {
         if (is_bf16 && out_bf16) MU_MOE(bf, bf, true);
         if (is_bf16) MU_MOE(bf, float, true);
@@ -324,10 +357,17 @@ MU_EXPORT int mu_moe_gemm(const void* x, long long ldx, const int* pair_of, int 
 #undef MU_MOE
 }
 
+// x (the experts' input rows, bfloat16 if x_bf16 else float32) is needed when a pair may have no slot.
 MU_EXPORT int mu_moe_combine(const float* y, long long ldy, const int* slot_of, const float* weight_of, int n_tokens,
-                             int top, int width, float* out, long long ldo, void* stream) {
+                             int top, int width, float* out, long long ldo, void* stream, const void* x, long long ldx,
+                             int x_bf16, const float* shared, long long lds, const float* shared_gate, int add) {
     if (n_tokens <= 0) return MU_OK;
     if (!y || !slot_of || !weight_of || !out || top <= 0 || width <= 0) return MU_ERR_BAD_ARGUMENT;
-    return mu::launch_pdl(mu::moe_combine_kernel, dim3(n_tokens), dim3(width >= 1024 ? 256 : 128), 0,
-                          (cudaStream_t)stream, 1, y, ldy, slot_of, weight_of, top, width, out, ldo);
+    const dim3 grid(n_tokens), block(width >= 1024 ? 256 : 128);
+    if (x_bf16)
+        return mu::launch_pdl(mu::moe_combine_kernel<__nv_bfloat16>, grid, block, 0, (cudaStream_t)stream, 1, y, ldy,
+                              slot_of, weight_of, top, width, out, ldo, (const __nv_bfloat16*)x, ldx, shared, lds,
+                              shared_gate, add);
+    return mu::launch_pdl(mu::moe_combine_kernel<float>, grid, block, 0, (cudaStream_t)stream, 1, y, ldy, slot_of,
+                          weight_of, top, width, out, ldo, (const float*)x, ldx, shared, lds, shared_gate, add);
 }

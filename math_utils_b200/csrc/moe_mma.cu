@@ -48,7 +48,7 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const in
                     const __nv_bfloat16* __restrict__ w1, const __nv_bfloat16* __restrict__ w2, long long expert_stride,
                     long long ldw, const int* __restrict__ tile_info, const int* __restrict__ n_tiles, int n, int k,
                     TO* __restrict__ out, long long ldo, int n_rows, long long x_group_offset,
-                    long long out_group_offset, const __nv_bfloat16* __restrict__ gate, long long ldg) {
+                    long long out_group_offset, const __nv_bfloat16* __restrict__ gate, long long ldg, int act) {
     extern __shared__ __align__(16) unsigned char mm_raw[];
     constexpr int MM_ROWS = 32 * WM, NW = 2 * WM;                               // rows a block; 8-column tiles a warp
     constexpr int STAGE = (MM_ROWS + (GATED ? 2 : 1) * MM_COLS) * MM_PITCH;      // elements per stage
@@ -159,6 +159,9 @@ moe_gemm_mma_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const in
                 if (GATED) {
                     v0 = v0 / (1.0f + expf(-v0)) * acc2[m][j][2 * half];
                     v1 = v1 / (1.0f + expf(-v1)) * acc2[m][j][2 * half + 1];
+                } else if (act == ACT_RELU2) {
+                    v0 = relu2(v0);
+                    v1 = relu2(v1);
                 }
                 if (gate) {                                      // out *= sigmoid(gate), in float32
                     const __nv_bfloat16* gp = gate + (long long)(slot0 + r) * ldg + col;
@@ -176,7 +179,7 @@ int launch_moe_mma(dim3 grid, cudaStream_t s, const __nv_bfloat16* x, long long 
                    const __nv_bfloat16* w1, const __nv_bfloat16* w2, long long expert_stride, long long ldw,
                    const int* tile_info, const int* n_tiles, int n, int k, TO* out, long long ldo, int n_rows = 0,
                    long long x_group_offset = 0, long long out_group_offset = 0, const __nv_bfloat16* gate = nullptr,
-                   long long ldg = 0) {
+                   long long ldg = 0, int act = 0) {
     constexpr size_t smem = MM_STAGES * (32 * WM + (GATED ? 2 : 1) * MM_COLS) * MM_PITCH * sizeof(__nv_bfloat16);
     static bool set = false;
     if (!set) {
@@ -187,7 +190,7 @@ int launch_moe_mma(dim3 grid, cudaStream_t s, const __nv_bfloat16* x, long long 
     }
     return launch_pdl(moe_gemm_mma_kernel<TO, GATED, WM>, grid, dim3(MM_THREADS), smem, s, 1, x, ldx, pair_of, top, w1, w2,
                       expert_stride, ldw, tile_info, n_tiles, n, k, out, ldo, n_rows, x_group_offset, out_group_offset, gate,
-                      ldg);
+                      ldg, act);
 }
 
 }  // namespace mu
@@ -196,22 +199,25 @@ int launch_moe_mma(dim3 grid, cudaStream_t s, const __nv_bfloat16* x, long long 
 MU_EXPORT int mu_moe_gemm_mma(const void* x, long long ldx, const int* pair_of, int top, const void* w1, const void* w2,
                               long long expert_stride, long long ldw, const int* tile_info, const int* n_tiles,
                               int max_tiles, int tile_rows, int n, int k, void* out, long long ldo, int out_bf16,
-                              void* stream) {
+                              void* stream, int act) {
     if (max_tiles <= 0) return MU_OK;
     if (!x || !w1 || !tile_info || !n_tiles || !out || n <= 0 || k <= 0 || (pair_of && top <= 0) ||
         (tile_rows != 32 && tile_rows != 64))
         return MU_ERR_BAD_ARGUMENT;
     if (k % 8 || ldx % 8 || ldw % 8 || expert_stride % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w1 & 15) || ((uintptr_t)w2 & 15))
         return MU_ERR_ALIGNMENT;
+    if (act != mu::ACT_NONE && act != mu::ACT_RELU2) return MU_ERR_BAD_ARGUMENT;
     cudaStream_t s = (cudaStream_t)stream;
     const dim3 grid(max_tiles, (n + mu::MM_COLS - 1) / mu::MM_COLS);
     typedef __nv_bfloat16 bf;
 #define MU_MM(TO, G)                                                                                                \
     return tile_rows == 64                                                                                          \
                ? mu::launch_moe_mma<TO, G, 2>(grid, s, (const bf*)x, ldx, pair_of, top, (const bf*)w1, (const bf*)w2, \
-                                              expert_stride, ldw, tile_info, n_tiles, n, k, (TO*)out, ldo)          \
+                                              expert_stride, ldw, tile_info, n_tiles, n, k, (TO*)out, ldo, 0, 0, 0,  \
+                                              nullptr, 0, act)                                                      \
                : mu::launch_moe_mma<TO, G, 1>(grid, s, (const bf*)x, ldx, pair_of, top, (const bf*)w1, (const bf*)w2, \
-                                              expert_stride, ldw, tile_info, n_tiles, n, k, (TO*)out, ldo)
+                                              expert_stride, ldw, tile_info, n_tiles, n, k, (TO*)out, ldo, 0, 0, 0,  \
+                                              nullptr, 0, act)
     if (w2) {
         if (out_bf16) MU_MM(bf, true);
         MU_MM(float, true);

@@ -5,6 +5,8 @@
 //                float32 residual stream); input always float32, output float32 or the compute dtype.
 // rms_norm:      y = x / sqrt(mean(x^2) + eps) * w, statistics in float32.
 // sigmoid_gate:  o *= 1 / (1 + exp(-g)), element by element, in float32.
+// rms_norm_pair: two RMS norms of the same rows (one statistic, two weights, two outputs).
+// softcap:       x <- cap * tanh(x / cap) on float32 rows, in place.
 #include "common.cuh"
 
 #include <math.h>
@@ -155,6 +157,76 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ o, long long ldo, const T* _
     }
 }
 
+// Two RMS norms of the same rows with the same eps: one pass over x, one statistic, two weights, two outputs.
+template <typename TO>
+__global__ void __launch_bounds__(256)
+rms_norm_pair_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ w1,
+                     const float* __restrict__ w2, float eps, TO* __restrict__ y1, long long ldy1,
+                     TO* __restrict__ y2, long long ldy2, int n, int vec) {
+    __shared__ float scratch[32];
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const float* src = x + (long long)r * ldx;
+    float s = 0.0f;
+    if (vec) {
+        // up to 4096 entries: a thread keeps its four float4 between the two passes
+        const float4* src4 = reinterpret_cast<const float4*>(src);
+        const int n4 = n / 4;
+        float4 v[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + 256 * i;
+            v[i] = idx < n4 ? src4[idx] : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            s += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+        }
+        const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)n + eps);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + 256 * i;
+            if (idx >= n4) continue;
+            const float4 a = reinterpret_cast<const float4*>(w1)[idx], b = reinterpret_cast<const float4*>(w2)[idx];
+            const float4 u = make_float4(v[i].x * inv, v[i].y * inv, v[i].z * inv, v[i].w * inv);
+            const float4 o1 = make_float4(u.x * a.x, u.y * a.y, u.z * a.z, u.w * a.w);
+            const float4 o2 = make_float4(u.x * b.x, u.y * b.y, u.z * b.z, u.w * b.w);
+            if (sizeof(TO) == 4) {
+                reinterpret_cast<float4*>(y1 + (long long)r * ldy1)[idx] = o1;
+                reinterpret_cast<float4*>(y2 + (long long)r * ldy2)[idx] = o2;
+            } else {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(o1.x, o1.y), p1 = __floats2bfloat162_rn(o1.z, o1.w);
+                __nv_bfloat162 q0 = __floats2bfloat162_rn(o2.x, o2.y), q1 = __floats2bfloat162_rn(o2.z, o2.w);
+                uint2 pa, pb;
+                pa.x = *reinterpret_cast<uint32_t*>(&p0); pa.y = *reinterpret_cast<uint32_t*>(&p1);
+                pb.x = *reinterpret_cast<uint32_t*>(&q0); pb.y = *reinterpret_cast<uint32_t*>(&q1);
+                reinterpret_cast<uint2*>(y1 + (long long)r * ldy1)[idx] = pa;
+                reinterpret_cast<uint2*>(y2 + (long long)r * ldy2)[idx] = pb;
+            }
+        }
+        return;
+    }
+    for (int d = threadIdx.x; d < n; d += blockDim.x) s += src[d] * src[d];
+    const float inv = 1.0f / sqrtf(block_sum(s, scratch) / (float)n + eps);
+    for (int d = threadIdx.x; d < n; d += blockDim.x) {
+        const float u = src[d] * inv;
+        y1[(long long)r * ldy1 + d] = from_float<TO>(u * w1[d]);
+        y2[(long long)r * ldy2 + d] = from_float<TO>(u * w2[d]);
+    }
+}
+
+// x <- cap * tanh(x / cap), float32 rows in place.
+__global__ void softcap_kernel(float* __restrict__ x, long long ldx, int n_rows, int width, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    const long long total = (long long)n_rows * width;
+    const float inv = 1.0f / cap;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / width;
+        const int c = (int)(i % width);
+        x[r * ldx + c] = cap * tanhf(x[r * ldx + c] * inv);
+    }
+}
+
 }  // namespace mu
 
 // y (+)= tanh(alpha x) w + b for n_rows rows (optionally the rows that `rows` picks from x).
@@ -237,4 +309,30 @@ MU_EXPORT int mu_sigmoid_gate(void* o, long long ldo, const void* g, long long l
                               (const __nv_bfloat16*)g, ldg, n_rows, width);
     return mu::launch_pdl(mu::sigmoid_gate_kernel<float>, grid, block, 0, s, 1, (float*)o, ldo, (const float*)g, ldg,
                           n_rows, width);
+}
+
+// y1 = rms_norm(x) * w1 and y2 = rms_norm(x) * w2 (same eps) of float32 rows; both outputs float32 or both bfloat16.
+MU_EXPORT int mu_rms_norm_pair(const float* x, long long ldx, const float* w1, const float* w2, float eps, void* y1,
+                               long long ldy1, void* y2, long long ldy2, int y_bf16, int n_rows, int n, void* stream) {
+    if (n_rows <= 0) return MU_OK;
+    if (n <= 0 || !x || !w1 || !w2 || !y1 || !y2) return MU_ERR_BAD_ARGUMENT;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int vec = n % 4 == 0 && n <= 4096 && ldx % 4 == 0 && ldy1 % 4 == 0 && ldy2 % 4 == 0 && ((uintptr_t)x & 15) == 0 &&
+                    ((uintptr_t)w1 & 15) == 0 && ((uintptr_t)w2 & 15) == 0 && ((uintptr_t)y1 & 15) == 0 &&
+                    ((uintptr_t)y2 & 15) == 0;
+    const dim3 grid(n_rows), block(256);
+    if (y_bf16)
+        return mu::launch_pdl(mu::rms_norm_pair_kernel<__nv_bfloat16>, grid, block, 0, s, 1, x, ldx, w1, w2, eps,
+                              (__nv_bfloat16*)y1, ldy1, (__nv_bfloat16*)y2, ldy2, n, vec);
+    return mu::launch_pdl(mu::rms_norm_pair_kernel<float>, grid, block, 0, s, 1, x, ldx, w1, w2, eps, (float*)y1, ldy1,
+                          (float*)y2, ldy2, n, vec);
+}
+
+// x <- cap * tanh(x / cap) on float32 rows, in place.
+MU_EXPORT int mu_softcap(float* x, long long ldx, int n_rows, int width, float cap, void* stream) {
+    if (n_rows <= 0 || width <= 0) return MU_OK;
+    if (!x || !(cap > 0.0f)) return MU_ERR_BAD_ARGUMENT;
+    const long long total = (long long)n_rows * width;
+    const dim3 grid((unsigned)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256)), block(256);
+    return mu::launch_pdl(mu::softcap_kernel, grid, block, 0, (cudaStream_t)stream, 1, x, ldx, n_rows, width, cap);
 }

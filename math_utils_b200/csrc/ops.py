@@ -16,7 +16,7 @@ import torch
 
 from . import build
 
-ACT_CODES = {None: 0, "none": 0, "gelu_new": 1, "gelu": 2}
+ACT_CODES = {None: 0, "none": 0, "gelu_new": 1, "gelu": 2, "relu2": 4}      # relu2: max(z, 0)^2
 GATE_ACT_CODES = {"gelu_new": 1, "gelu": 2, "silu": 3}       # what a gated feed-forward may put on its gate
 
 _ERRORS = {
@@ -93,19 +93,19 @@ _SIGNATURES = {
     "mu_scaled_sum": [_c_p, _c_ll, _c_f, _c_p, _c_ll, _c_f, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
     "mu_cast_rows": [_c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_p],
     "mu_qk_prepare": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_f, _c_int, _c_f, _c_int, _c_int, _c_int,
-                      _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p],
+                      _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p, _c_int],
     "mu_mapped_attention": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                             _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_int, _c_p,
-                            _c_p, _c_int, _c_p, _c_ll],
+                            _c_p, _c_int, _c_p, _c_ll, _c_int],
     "mu_mapped_decode_fits": [_c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int],
     "mu_mapped_decode_scratch": [_c_int, _c_int, _c_int, _c_int],
     "mu_mapped_attention_decode": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int,
                                    _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_p, _c_ll, _c_int, _c_p,
-                                   _c_p, _c_int, _c_p, _c_ll],
+                                   _c_p, _c_int, _c_p, _c_ll, _c_int],
     "mu_mapped_attention_mma_fits": [_c_int, _c_int, _c_int, _c_int, _c_int],
     "mu_mapped_attention_mma": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int,
                                 _c_int, _c_int, _c_f, _c_int, _c_f, _c_f, _c_f, _c_int, _c_p, _c_ll, _c_p,
-                                _c_p, _c_int, _c_p, _c_ll],
+                                _c_p, _c_int, _c_p, _c_ll, _c_int],
     "mu_qkv_norm_rows": [_c_p, _c_ll, _c_p, _c_ll, _c_p, _c_ll, _c_p, _c_p, _c_f, _c_int, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_p, _c_int, _c_f, _c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_int, _c_p],
     "mu_residual_add_norm": [_c_p, _c_ll, _c_p, _c_ll, _c_f, _c_p, _c_f, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p],
@@ -126,24 +126,27 @@ _SIGNATURES = {
     "mu_rotary": [_c_p, _c_ll, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_p, _c_f, _c_int, _c_int, _c_int,
                   _c_int, _c_p],
     "mu_latent_append": [_c_p, _c_ll, _c_p, _c_f, _c_p, _c_f, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int,
-                         _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_p],
+                         _c_int, _c_p, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_ll, _c_int, _c_int, _c_p, _c_int],
     "mu_moe_combine_tanh": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_ll, _c_p],
     "mu_latent_attention": [_c_p, _c_p, _c_p, _c_int, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int,
-                            _c_p, _c_ll, _c_p, _c_p, _c_int, _c_p],
-    "mu_latent_merge": [_c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p],
+                            _c_p, _c_ll, _c_p, _c_p, _c_int, _c_p, _c_p],
+    "mu_latent_merge": [_c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_p],
     "mu_latent_attention_mma_fits": [_c_int, _c_int, _c_int],
     "mu_latent_attention_mma": [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f,
-                                _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p],
+                                _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p],
     "mu_moe_route": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p,
-                     _c_p],
-    "mu_moe_group": [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p],
+                     _c_p, _c_f, _c_p, _c_p],
+    "mu_moe_group": [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int],
     "mu_moe_gemm": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll,
-                    _c_int, _c_int, _c_p],
+                    _c_int, _c_int, _c_p, _c_int],
     "mu_moe_gemm_mma": [_c_p, _c_ll, _c_p, _c_int, _c_p, _c_p, _c_ll, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p,
-                        _c_ll, _c_int, _c_p],
+                        _c_ll, _c_int, _c_p, _c_int],
     "mu_heads_gemm": [_c_p, _c_ll, _c_ll, _c_p, _c_ll, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_ll, _c_int,
                       _c_p, _c_ll, _c_p],
-    "mu_moe_combine": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_p],
+    "mu_moe_combine": [_c_p, _c_ll, _c_p, _c_p, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_p, _c_p, _c_ll, _c_int, _c_p,
+                       _c_ll, _c_p, _c_int],
+    "mu_rms_norm_pair": [_c_p, _c_ll, _c_p, _c_p, _c_f, _c_p, _c_ll, _c_p, _c_ll, _c_int, _c_int, _c_int, _c_p],
+    "mu_softcap": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_p],
     "mu_moe_tile_rows": [],
     "mu_sample": [_c_p, _c_ll, _c_int, _c_int, _c_f, _c_int, _c_ull, _c_p, _c_p, _c_p, _c_p, _c_p, _c_int,
                   _c_p, _c_p, _c_p],
@@ -449,12 +452,15 @@ def embed_pair(ids: torch.Tensor, positions: torch.Tensor, tok_seq: torch.Tensor
 
 
 # ------------------------------------------------------------------ attention over cached rows with score maps
-def qk_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_weight: torch.Tensor,
+def qk_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Tensor], q_weight: Optional[torch.Tensor],
                k_weight: Optional[torch.Tensor], freqs: torch.Tensor, magnitude: float, rot_dims: int, eps: float,
                n_heads: int, n_kv_heads: int, maps: int, dim: int, vdim: int, tok_pos, tok_seq,
-               block_table: Optional[torch.Tensor], page_tokens: int, rows: Optional[torch.Tensor]) -> None:
+               block_table: Optional[torch.Tensor], page_tokens: int, rows: Optional[torch.Tensor],
+               pairs: bool = False) -> None:
     """Unit rms times a weight, then the rotation, for every (head, map) slice of the queries (in place) and of the
-    keys (into the token's cache row, with the values behind them).  ``k`` and ``v`` None: queries only."""
+    keys (into the token's cache row, with the values behind them).  ``k`` and ``v`` None: queries only.
+    Without weights (both None) the slices are not normed.  ``pairs``: entry 2i turns with entry 2i + 1 instead of
+    entry i with entry i + rot_dims / 2."""
     _need_cuda(q, k, v, q_weight, k_weight, freqs, tok_pos, tok_seq, block_table, rows)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -473,7 +479,7 @@ def qk_prepare(q: torch.Tensor, k: Optional[torch.Tensor], v: Optional[torch.Ten
                                    float(magnitude), int(rot_dims), float(eps), q.shape[0], int(n_heads),
                                    int(n_kv_heads), int(maps), int(dim), int(vdim), _ptr(tok_pos), _ptr(tok_seq),
                                    _ptr(block_table), block_table.shape[1] if block_table is not None else 0,
-                                   int(page_tokens), _ptr(rows), _is_bf16(q), _stream()),
+                                   int(page_tokens), _ptr(rows), _is_bf16(q), _stream(), int(pairs)),
            ("qk_prepare(dim={}, maps={})", dim, maps))
 
 
@@ -483,7 +489,7 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
                      unit_rms: bool = False, tiles: Optional[torch.Tensor] = None,
                      tensor_cores: Optional[bool] = None, single_tokens: bool = False,
                      head_scale: Optional[torch.Tensor] = None, sink: bool = False,
-                     gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     gate: Optional[torch.Tensor] = None, chunk: int = 0) -> torch.Tensor:
     """Softmax attention of every (token, head) over the cached rows it sees (``window`` 0: all up to its own
     position), one result per score map over the same values; with two maps a1 - lam * a2.  ``unit_rms`` brings
     each head's result to unit rms (eps inside the root); ``out_scale`` multiplies it.
@@ -495,7 +501,8 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
 
     ``head_scale`` (float32, one per head) multiplies the head's scores besides ``scale``; ``sink`` adds to the
     softmax's denominator one key of score zero that has no value; ``gate`` ([T, heads] view in the compute dtype)
-    multiplies each head's result by sigmoid(gate[t, h])."""
+    multiplies each head's result by sigmoid(gate[t, h]); ``chunk`` c > 0 replaces the window: position p sees
+    p - p % c .. p."""
     _need_cuda(q, rows, block_table, tok_pos, tok_seq, out, head_scale, gate)
     if head_scale is not None and (head_scale.dtype != torch.float32 or head_scale.numel() != n_heads
                                    or not head_scale.is_contiguous()):
@@ -503,7 +510,7 @@ def mapped_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
     if gate is not None and (gate.dtype != rows.dtype or gate.dim() != 2 or gate.shape != (q.shape[0], n_heads)
                              or gate.stride(1) != 1):
         raise KernelError("mapped_attention: the gate is [T, heads] in the compute dtype with unit inner stride")
-    extras = (_ptr(head_scale), int(sink), _ptr(gate), gate.stride(0) if gate is not None else 0)
+    extras = (_ptr(head_scale), int(sink), _ptr(gate), gate.stride(0) if gate is not None else 0, int(chunk))
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
     if (q.dtype != rows.dtype or out.dtype != rows.dtype or q.stride(1) != 1 or out.stride(1) != 1
@@ -744,13 +751,15 @@ def rotary(x: torch.Tensor, out: torch.Tensor, tok_pos: torch.Tensor, freqs: tor
 
 def latent_append(dkv: Optional[torch.Tensor], norm_weight: Optional[torch.Tensor], eps: float, freqs: torch.Tensor,
                   magnitude: float, rot_dims: int, kv_rank: int, rot_dim: int, tok_pos, tok_seq,
-                  block_table: torch.Tensor, page_tokens: int, rows: torch.Tensor, queries=None) -> None:
+                  block_table: torch.Tensor, page_tokens: int, rows: torch.Tensor, queries=None,
+                  pairs: bool = False) -> None:
     """Per token: the RMS norm of the first ``kv_rank`` values of ``dkv`` and the rotation of the last ``rot_dim``
     go to the token's row of the latent cache ``rows`` [pages, page_tokens, kv_rank + rot_dim].
 
     ``queries`` = (q, q_head_stride, qa, qa_head_stride, n_heads): the same launch rotates every head's ``rot_dim``
     entries (views whose first element is head 0's first rotated entry) from ``q`` into the float32 ``qa``.  With
-    ``dkv`` None only that is done (a layer that reads another layer's cache)."""
+    ``dkv`` None only that is done (a layer that reads another layer's cache).  ``pairs``: entry 2i turns with
+    entry 2i + 1 instead of entry i with entry i + rot_dims / 2."""
     _need_cuda(dkv, norm_weight, freqs, tok_pos, tok_seq, block_table, rows)
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -774,7 +783,8 @@ def latent_append(dkv: Optional[torch.Tensor], norm_weight: Optional[torch.Tenso
                                       _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), block_table.shape[1],
                                       int(page_tokens), n_tokens, _ptr(rows), _is_bf16(rows), _ptr(q),
                                       q.stride(0) if q is not None else 0, int(qs), _ptr(qa),
-                                      qa.stride(0) if qa is not None else 0, int(qas), int(heads), _stream()),
+                                      qa.stride(0) if qa is not None else 0, int(qas), int(heads), _stream(),
+                                      int(pairs)),
            "latent_append")
 
 
@@ -782,15 +792,18 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
                      n_heads: int, kv_rank: int, scale: float, out: torch.Tensor, n_splits: int = 1,
                      part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
                      tiles: Optional[torch.Tensor] = None, single_tokens: bool = False,
-                     tensor_cores: Optional[bool] = None) -> torch.Tensor:
+                     tensor_cores: Optional[bool] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of float32 queries [T, n_heads, width] over the latent rows 0..position of each token's sequence;
     ``out`` [T, n_heads * kv_rank] receives the weighted sums of the rows' first ``kv_rank`` values.
 
     bfloat16 caches at the sizes ``mu_latent_attention_mma`` takes go to the tensor cores when the step says how its
     tokens group: ``tiles`` (int32 [n, 2]: first flat token and count <= 64 of runs of tokens of one sequence) or
     ``single_tokens`` (every token is the one token of its sequence); ``tensor_cores`` false keeps the CUDA-core
-    kernel.  ``n_splits`` > 1 (single-token steps) cuts each sequence's rows into parts that are merged afterwards."""
-    _need_cuda(q, rows, block_table, tok_pos, tok_seq, out, part_o, part_ml, tiles)
+    kernel.  ``n_splits`` > 1 (single-token steps) cuts each sequence's rows into parts that are merged afterwards.
+    ``sink`` (float32, one per head): exp(sink[h]) is added to head h's softmax denominator, with no value behind it."""
+    _need_cuda(q, rows, block_table, tok_pos, tok_seq, out, part_o, part_ml, tiles, sink)
+    if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
+        raise KernelError("latent_attention: the sink is one contiguous float32 per head")
     _i32(tiles, "tiles")
     for t, name in ((tok_pos, "tok_pos"), (tok_seq, "tok_seq"), (block_table, "block_table")):
         _i32(t, name)
@@ -815,15 +828,15 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
         _check(library().mu_latent_attention_mma(
             _ptr(q), _ptr(rows), _ptr(block_table), block_table.shape[1], _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles),
             tiles.shape[0] if tiles is not None else 0, n_tokens, int(n_heads), int(kv_rank), int(width), float(scale),
-            int(n_splits), _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _stream()), what)
+            int(n_splits), _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _stream(), _ptr(sink)), what)
         if n_splits > 1:
             _check(library().mu_latent_merge(_ptr(part_o), _ptr(part_ml), n_tokens, int(n_heads), int(kv_rank),
-                                             int(n_splits), _ptr(out), out.stride(0), 1, _stream()), what)
+                                             int(n_splits), _ptr(out), out.stride(0), 1, _stream(), _ptr(sink)), what)
         return out
     _check(library().mu_latent_attention(_ptr(q), _ptr(rows), _ptr(block_table), block_table.shape[1], int(page_tokens),
                                          _ptr(tok_pos), _ptr(tok_seq), n_tokens, int(n_heads), int(kv_rank), int(width),
                                          float(scale), int(n_splits), _ptr(out), out.stride(0), _ptr(part_o),
-                                         _ptr(part_ml), _is_bf16(rows), _stream()),
+                                         _ptr(part_ml), _is_bf16(rows), _stream(), _ptr(sink)),
            ("latent_attention(heads={}, kv_rank={}, width={})", n_heads, kv_rank, width),
            launches=2 if n_splits > 1 else 1)
     return out
@@ -835,10 +848,20 @@ def moe_tile_rows() -> int:
 
 
 def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, scale: float,
-              expert_of: torch.Tensor, weight_of: torch.Tensor, softmax: bool = False, renormalize: bool = False) -> None:
+              expert_of: torch.Tensor, weight_of: torch.Tensor, softmax: bool = False, renormalize: bool = False,
+              renorm_eps: float = 0.0, gate_weight: Optional[torch.Tensor] = None,
+              gate_out: Optional[torch.Tensor] = None) -> None:
     """Router of a feed-forward of experts: logits in float32 from the rows of ``h``, sigmoid (or softmax) scores,
-    the ``top`` experts by score + correction into ``expert_of`` [T, top] int32, score * scale into ``weight_of``."""
-    _need_cuda(h, router, correction, expert_of, weight_of)
+    the ``top`` experts by score + correction into ``expert_of`` [T, top] int32, score * scale into ``weight_of``
+    (with ``renormalize`` divided by the chosen scores' sum + ``renorm_eps``).  ``gate_weight`` (float32 [hidden])
+    with ``gate_out`` (float32 [T]): the same launch leaves sigmoid(gate_weight . h) per token, a shared expert's gate."""
+    _need_cuda(h, router, correction, expert_of, weight_of, gate_weight, gate_out)
+    if (gate_weight is None) != (gate_out is None):
+        raise KernelError("moe_route: a shared expert's gate needs its weight and a place for the result")
+    if gate_weight is not None and (gate_weight.dtype != torch.float32 or not gate_weight.is_contiguous()
+                                    or gate_weight.numel() != h.shape[1] or gate_out.dtype != torch.float32
+                                    or gate_out.numel() < h.shape[0] or not gate_out.is_contiguous()):
+        raise KernelError("moe_route: the gate weight is float32 [hidden], its result float32 [T]")
     n_experts, hidden = router.shape
     if router.dtype != torch.float32 or not router.is_contiguous() or h.shape[1] != hidden or h.stride(1) != 1:
         raise KernelError("moe_route takes rows [T, hidden] and a contiguous float32 router [experts, hidden]")
@@ -847,7 +870,8 @@ def moe_route(h: torch.Tensor, router: torch.Tensor, correction: Optional[torch.
     _i32(expert_of, "expert_of")
     _check(library().mu_moe_route(_ptr(h), h.stride(0), _is_bf16(h), _ptr(router), _ptr(correction), h.shape[0], hidden,
                                   n_experts, int(top), float(scale), int(softmax), int(renormalize), _ptr(expert_of),
-                                  _ptr(weight_of), _stream()), ("moe_route(experts={}, top={})", n_experts, top))
+                                  _ptr(weight_of), _stream(), float(renorm_eps), _ptr(gate_weight), _ptr(gate_out)),
+           ("moe_route(experts={}, top={})", n_experts, top))
 
 
 def moe_tc_ok(x_dtype: torch.dtype, k1: int, k2: int) -> bool:
@@ -856,22 +880,25 @@ def moe_tc_ok(x_dtype: torch.dtype, k1: int, k2: int) -> bool:
 
 
 def moe_group(expert_of: torch.Tensor, n_experts: int, slot_of: torch.Tensor, pair_of: torch.Tensor,
-              tile_info: torch.Tensor, n_tiles: torch.Tensor, tile_rows: int = 0) -> None:
+              tile_info: torch.Tensor, n_tiles: torch.Tensor, tile_rows: int = 0, n_real: int = 0) -> None:
     """Groups the (token, expert) pairs by expert: a slot per pair, and the list of tiles of up to ``tile_rows``
-    slots per expert (0: the CUDA-core product's tile)."""
+    slots per expert (0: the CUDA-core product's tile).  ``n_real`` > 0: the experts from ``n_real`` on have no
+    matrices (identity experts); their pairs get slot -1 and no tile."""
     _need_cuda(expert_of, slot_of, pair_of, tile_info, n_tiles)
     for t, name in ((expert_of, "expert_of"), (slot_of, "slot_of"), (pair_of, "pair_of"), (tile_info, "tile_info"),
                     (n_tiles, "n_tiles")):
         _i32(t, name)
     _check(library().mu_moe_group(_ptr(expert_of), expert_of.numel(), int(n_experts), _ptr(slot_of), _ptr(pair_of),
-                                  _ptr(tile_info), _ptr(n_tiles), int(tile_rows) or moe_tile_rows(), _stream()),
+                                  _ptr(tile_info), _ptr(n_tiles), int(tile_rows) or moe_tile_rows(), _stream(),
+                                  int(n_real)),
            "moe_group")
 
 
 def moe_gemm(x: torch.Tensor, pair_of: Optional[torch.Tensor], top: int, w1: torch.Tensor, w2: Optional[torch.Tensor],
              tile_info: torch.Tensor, n_tiles: torch.Tensor, max_tiles: int, out: torch.Tensor,
-             tensor_cores: Optional[bool] = None, tile_rows: int = 0) -> torch.Tensor:
-    """out[slot] = W1[e] x[row] (or silu(W1[e] x[row]) * W2[e] x[row] with ``w2``) for every slot of every expert e;
+             tensor_cores: Optional[bool] = None, tile_rows: int = 0, act: Optional[str] = None) -> torch.Tensor:
+    """out[slot] = act(W1[e] x[row]) (or silu(W1[e] x[row]) * W2[e] x[row] with ``w2``) for every slot of every expert e
+    (``act``: None or ``relu2``);
     ``w1``/``w2`` [experts, n, k]; rows of ``x`` by the slot's token (``pair_of``) or by slot.  bfloat16 operands
     with 16-byte aligned rows go to the tensor cores unless ``tensor_cores`` is false.  ``tile_rows``: what
     ``moe_group`` was given (the CUDA-core product takes its own tile only)."""
@@ -884,20 +911,23 @@ def moe_gemm(x: torch.Tensor, pair_of: Optional[torch.Tensor], top: int, w1: tor
         raise KernelError("moe_gemm output has the wrong shape or stride")
     if tensor_cores is None:
         tensor_cores = LATENT_TC
+    if act not in (None, "none", "relu2") or (act == "relu2" and w2 is not None):
+        raise KernelError(f"moe_gemm: activation '{act}' is not taken (relu2 without a second weight stack, or none)")
+    code = ACT_CODES[act]
     tile_rows = int(tile_rows) or moe_tile_rows()
     if (tensor_cores and x.dtype == torch.bfloat16 and w1.shape[2] % 8 == 0 and x.stride(0) % 8 == 0
             and x.data_ptr() % 16 == 0 and w1.data_ptr() % 16 == 0 and (w2 is None or w2.data_ptr() % 16 == 0)):
         _check(library().mu_moe_gemm_mma(_ptr(x), x.stride(0), _ptr(pair_of), int(top), _ptr(w1), _ptr(w2),
                                          w1.stride(0), w1.stride(1), _ptr(tile_info), _ptr(n_tiles), int(max_tiles),
                                          tile_rows, w1.shape[1], w1.shape[2], _ptr(out), out.stride(0), _is_bf16(out),
-                                         _stream()), ("moe_gemm_mma(n={}, k={})", w1.shape[1], w1.shape[2]))
+                                         _stream(), code), ("moe_gemm_mma(n={}, k={})", w1.shape[1], w1.shape[2]))
         return out
     if tile_rows != moe_tile_rows():
         raise KernelError(f"the CUDA-core experts' product takes tiles of {moe_tile_rows()} slots, got {tile_rows}")
     _check(library().mu_moe_gemm(_ptr(x), x.stride(0), _ptr(pair_of), int(top), _ptr(w1), _ptr(w2),
                                  w1.stride(0), w1.stride(1), _ptr(tile_info), _ptr(n_tiles), int(max_tiles),
                                  w1.shape[1], w1.shape[2], _ptr(out), out.stride(0), _is_bf16(x), _is_bf16(out),
-                                 _stream()), ("moe_gemm(n={}, k={})", w1.shape[1], w1.shape[2]))
+                                 _stream(), code), ("moe_gemm(n={}, k={})", w1.shape[1], w1.shape[2]))
     return out
 
 
@@ -928,14 +958,57 @@ def heads_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, x_head_strid
     return out
 
 
-def moe_combine(y: torch.Tensor, slot_of: torch.Tensor, weight_of: torch.Tensor, top: int, out: torch.Tensor) -> torch.Tensor:
-    """out[t] = sum over the token's choices, in their order, of weight * y[slot]; float32."""
-    _need_cuda(y, slot_of, weight_of, out)
+def moe_combine(y: torch.Tensor, slot_of: torch.Tensor, weight_of: torch.Tensor, top: int, out: torch.Tensor,
+                identity_rows: Optional[torch.Tensor] = None, shared: Optional[torch.Tensor] = None,
+                shared_gate: Optional[torch.Tensor] = None, add: bool = False) -> torch.Tensor:
+    """out[t] (+)= sum over the token's choices, in their order, of weight * y[slot]; float32.  A choice without a
+    slot (an identity expert, slot -1) contributes weight * ``identity_rows[t]`` (the experts' input rows, compute
+    dtype).  ``shared`` (float32 [T, width]) is added to every token, times ``shared_gate[t]`` if given.  ``add``:
+    the result is added to what ``out`` holds."""
+    _need_cuda(y, slot_of, weight_of, out, identity_rows, shared, shared_gate)
     if y.dtype != torch.float32 or out.dtype != torch.float32 or y.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("moe_combine works on float32 rows with unit inner stride")
+    if identity_rows is not None and (identity_rows.shape != out.shape or identity_rows.stride(1) != 1):
+        raise KernelError("moe_combine: the identity rows are shaped like the output, unit inner stride")
+    if shared is not None and (shared.dtype != torch.float32 or shared.shape != out.shape or shared.stride(1) != 1):
+        raise KernelError("moe_combine: the shared expert's rows are float32 and shaped like the output")
+    if shared_gate is not None and (shared is None or shared_gate.dtype != torch.float32 or not shared_gate.is_contiguous()
+                                    or shared_gate.numel() < out.shape[0]):
+        raise KernelError("moe_combine: the shared expert's gate is float32 [T] and needs the shared rows")
     _check(library().mu_moe_combine(_ptr(y), y.stride(0), _ptr(slot_of), _ptr(weight_of), out.shape[0], int(top),
-                                    out.shape[1], _ptr(out), out.stride(0), _stream()), "moe_combine")
+                                    out.shape[1], _ptr(out), out.stride(0), _stream(), _ptr(identity_rows),
+                                    identity_rows.stride(0) if identity_rows is not None else 0,
+                                    _is_bf16(identity_rows) if identity_rows is not None else 0, _ptr(shared),
+                                    shared.stride(0) if shared is not None else 0, _ptr(shared_gate), int(add)),
+           "moe_combine")
     return out
+
+
+def rms_norm_pair(x: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, eps: float, out1: torch.Tensor,
+                  out2: torch.Tensor) -> None:
+    """out1 = x / sqrt(mean(x^2) + eps) * w1 and out2 = the same rows * w2: two norms of one float32 stream in one
+    pass (one statistic).  Both outputs float32 or both bfloat16."""
+    _need_cuda(x, w1, w2, out1, out2)
+    n = x.shape[1]
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("rms_norm_pair input must be float32 [rows, n] with unit inner stride")
+    for w in (w1, w2):
+        if w.dtype != torch.float32 or not w.is_contiguous() or w.numel() != n:
+            raise KernelError("rms_norm_pair takes contiguous float32 weights of n values")
+    if out1.dtype != out2.dtype or out1.shape != x.shape or out2.shape != x.shape or out1.stride(1) != 1 or out2.stride(1) != 1:
+        raise KernelError("rms_norm_pair outputs are of one dtype and shaped like the input")
+    _check(library().mu_rms_norm_pair(_ptr(x), x.stride(0), _ptr(w1), _ptr(w2), float(eps), _ptr(out1), out1.stride(0),
+                                      _ptr(out2), out2.stride(0), _is_bf16(out1), x.shape[0], n, _stream()),
+           ("rms_norm_pair(n={})", n))
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) on float32 rows, in place."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1 or not cap > 0.0:
+        raise KernelError("softcap takes float32 [rows, n] with unit inner stride and a positive cap")
+    _check(library().mu_softcap(_ptr(x), x.stride(0), x.shape[0], x.shape[1], float(cap), _stream()), "softcap")
+    return x
 
 
 def moe_combine_tanh(y: torch.Tensor, slot_of: torch.Tensor, weight_of: torch.Tensor, top: int, weight: torch.Tensor,

@@ -21,6 +21,11 @@ layer without a feed-forward (kind ``none``) stops after the mixer.
 buffer; the addition to the stream is made by the launch of the NEXT norm (``ops.residual_add_norm``:
 x += m * y, then the normed row), also across layers (``StepContext.pending_join``), so the stream is
 read and written once per sublayer.
+
+``parallel_pre_norm``: x += mixer(norm1(x)) + feed_forward(norm2(x)), both sublayers reading the SAME x through a
+norm of their own.  Both norms are made before either sublayer adds into the stream (two RMS norms with one eps
+by one launch: one pass over x, one statistic, two weights); then the mixer and the feed-forward add into the
+float32 stream in their last launches.  A layer without a feed-forward is x += mixer(norm1(x)).
 """
 from __future__ import annotations
 
@@ -208,6 +213,29 @@ class ScaledPreNormBlock(Arrangement):
         return norm.forward(x)
 
 
+class ParallelPreNormBlock(Arrangement):
+    def forward(self, x, layer, ctx, cache, owns_cache: bool) -> None:
+        n1, n2 = layer.norm1, layer.norm2
+        alone = isinstance(layer.feed_forward, NoFeedForward)
+        if (not alone and type(n1) is RmsNorm and type(n2) is RmsNorm and n1.eps == n2.eps and x.stride(1) == 1
+                and n1.offset == n2.offset == 0.0 and n1.scale == n2.scale == 1.0):
+            dt = n1.runtime.dtype
+            h1 = ctx.buffer("stream.normed", tuple(x.shape), dt)
+            h2 = ctx.buffer("stream.normed2", tuple(x.shape), dt)
+            n1.runtime.ops.rms_norm_pair(x, n1.weight, n2.weight, n1.eps, h1, h2)
+        else:
+            h1 = n1.forward(x)
+            h2 = None if alone else n2.forward(x)         # before the mixer changes x
+        ctx.note("ln1", h1)
+        layer.mixer.forward(h1, x, ctx, cache, owns_cache)
+        ctx.note("res1", x)
+        if not alone:
+            ctx.note("ln2", h2)
+            layer.feed_forward.forward(h2, x, ctx)
+        ctx.note("res2", x)
+
+
 register_part("arrangement", "pre_norm", PreNormBlock, replace=True)
+register_part("arrangement", "parallel_pre_norm", ParallelPreNormBlock, replace=True)
 register_part("arrangement", "scaled_pre_norm", ScaledPreNormBlock, replace=True)
 register_part("arrangement", "sandwich_norm", SandwichNormBlock, replace=True)

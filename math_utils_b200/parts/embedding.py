@@ -97,13 +97,15 @@ class TiedHead(Head):
 
 
 class LinearHead(Head):
-    """Logits = h @ W^T with an output matrix ``weight`` [vocab, hidden] of its own, no bias."""
+    """Logits = h @ W^T with an output matrix ``weight`` [vocab, hidden] of its own, no bias.  With the
+    parameter ``softcap`` c > 0 the logits become c * tanh(logits / c)."""
     takes_lazy_norm = True
 
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         self.vocab_size = int(self.param("vocab_size"))
         self.hidden_size = int(self.param("hidden_size"))
+        self.softcap = float(self.param("softcap", 0.0) or 0.0)
 
     def tensor_specs(self):
         return (TensorSpec(self.tensor_name("weight"), (self.vocab_size, self.hidden_size), role="matrix"),)
@@ -115,7 +117,10 @@ class LinearHead(Head):
 
     def forward(self, h):
         import torch
-        return self.linear(h, out_dtype=torch.float32)
+        logits = self.linear(h, out_dtype=torch.float32)
+        if self.softcap > 0.0:
+            self.runtime.ops.softcap(logits, self.softcap)
+        return logits
 
 
 register_part("embedding", "token_embedding", TokenEmbedding, replace=True)

@@ -48,8 +48,16 @@ def rotary_frequencies(dims: int, base: float, scaling=None):
     the ``original`` one (the YaRN rule: Peng, Quesnelle, Fan, Shippole, "YaRN: Efficient Context Window
     Extension of Large Language Models"): with turns(t) = dims ln(original / (2 pi t)) / (2 ln base), the
     dimensions below lo = floor(turns(fast)) keep f_i, those above hi = ceil(turns(slow)) get f_i / factor,
-    a linear ramp lies between, and cos and sin are multiplied by 0.1 ln(factor) + 1.  Computed in
-    float64 here; the kernels take the table as float32."""
+    a linear ramp lies between, and cos and sin are multiplied by 0.1 ln(factor) + 1.
+
+    ``scaling`` = {factor, low, high, original} is the rule by wavelength bands (as Llama 3.1 scales its
+    frequencies): with l = 2 pi / f, a frequency keeps its value where l < original / high, becomes
+    f / factor where l > original / low, and in between is (1 - s) f / factor + s f with
+    s = (original / l - low) / (high - low); the magnitude stays 1.  Which rule applies follows from the
+    keys.  The order of the frequencies is that of the pairs, whatever the layout of a pair's two entries
+    (i with i + dims/2, or 2i with 2i + 1: the kernels take that as a switch).
+
+    Computed in float64 here; the kernels take the table as float32."""
     import math
     if dims < 0 or dims % 2:
         raise ConfigError(f"a rotary encoding turns an even number of entries, got {dims}")
@@ -58,6 +66,21 @@ def rotary_frequencies(dims: int, base: float, scaling=None):
     if not scaling:
         return freqs, 1.0
     factor, original = float(scaling["factor"]), float(scaling["original"])
+    if "low" in scaling or "high" in scaling:
+        low, high = float(scaling["low"]), float(scaling["high"])
+        if not high > low:
+            raise ConfigError("rotary scaling by wavelength bands needs high > low")
+        banded = []
+        for f in freqs:
+            length = 2.0 * math.pi / f
+            if length < original / high:
+                banded.append(f)
+            elif length > original / low:
+                banded.append(f / factor)
+            else:
+                s = (original / length - low) / (high - low)
+                banded.append((1.0 - s) * f / factor + s * f)
+        return banded, 1.0
 
     def turns(t):
         return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(base))
