@@ -92,7 +92,7 @@ def chunked_attention(h, w, p, m):
     from the mixer's own input, output projection with bias."""
     T = h.shape[0]
     H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    size = int(m["mask"]["size"])
+    size = int((m.get("mask") or {}).get("size", 0))               # no mask: every earlier position
     rot = m["rot"]
     freqs = rotary_frequencies(int(rot["dims"]), float(rot["base"]), rot.get("scaling"))
     pos = np.arange(T)
@@ -104,7 +104,7 @@ def chunked_attention(h, w, p, m):
     heads = np.zeros((T, H, dv), dtype=F)
     for a in range(H):
         g = a // (H // G)
-        heads[:, a] = masked_attention(q[:, a], k[:, g], v[:, g], float(m["scale"]), lambda i: i - i % size)
+        heads[:, a] = masked_attention(q[:, a], k[:, g], v[:, g], float(m["scale"]), lambda i: i - i % size if size else 0)
         heads[:, a] *= gate[:, a: a + 1]
     return heads.reshape(T, H * dv) @ w[p + "o"].T + w[p + "o.b"]
 
@@ -229,3 +229,73 @@ def read_model(model_dir):
             raise ValueError(f"{name}: dtype {info['dtype']}")
         w[name] = a.reshape(info["shape"]).astype(F)
     return config, w
+
+
+# ------------------------------------------------------------------ random models for the tests
+def tensor_shapes(config):
+    """name -> shape of every tensor a model of this configuration has (layers that use another layer's
+    tensors have none)."""
+    D, V = int(config["width"]), int(config["vocab"])
+    out = {"embed": (V, D), "final.norm": (D,), "head": (V, D)}
+    for i, layer in enumerate(config["layers"]):
+        if layer.get("weights_of") is not None:
+            continue
+        p, m = f"l{i}.", layer["mixer"]
+        out[p + "norm1"] = (D,)
+        x = p + "mix."
+        if layer["type"] == "attention":
+            H, G, d, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+            out.update({x + "q": (H * d, D), x + "q.b": (H * d,), x + "k": (G * d, D), x + "k.b": (G * d,),
+                        x + "v": (G * dv, D), x + "v.b": (G * dv,), x + "g": (H, D), x + "o": (D, H * dv), x + "o.b": (D,)})
+        else:
+            H, d, dr, dv = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"])
+            r, rq = int(m["kv_rank"]), int(m["q_rank"])
+            out.update({x + "dq": (rq, D), x + "dq.norm": (rq,), x + "uq": (H * (d + dr), rq), x + "dkv": (r + dr, D),
+                        x + "dkv.norm": (r,), x + "uk": (H * d, r), x + "uv": (H * dv, r), x + "sink": (H,),
+                        x + "o": (D, H * dv)})
+        f = layer.get("mlp")
+        if f is None:
+            continue
+        out[p + "norm2"] = (D,)
+        y = p + "mlp."
+        E, n_id, ff = int(f["router"]["experts"]), int(f["router"].get("identity") or 0), int(f["expert"]["ff"])
+        out[y + "router"], out[y + "correction"] = (E + n_id, D), (E + n_id,)
+        for e in range(E):
+            out[f"{y}e{e}.up"], out[f"{y}e{e}.down"] = (ff, D), (D, ff)
+        if f.get("shared"):
+            s = int(f["shared"]["ff"])
+            out.update({y + "shared.up": (s, D), y + "shared.down": (D, s), y + "shared.sg": (1, D)})
+    return out
+
+
+def to_bfloat16(a):
+    """The nearest values that bfloat16 holds (eight bits of mantissa, ties to even), as float64."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    bits = a.view(np.uint32).astype(np.uint64)
+    bits = ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16
+    return bits.astype(np.uint32).view(np.float32).astype(F).reshape(a.shape)
+
+
+def random_weights(config, seed, sharp=3.0):
+    """Weights that bfloat16 holds exactly (the tests write them to a bfloat16 file), sized so that every
+    mechanism matters: sinks that take a visible share, corrections that change choices, gates away from
+    one half, queries and keys ``sharp`` times larger than the rest for peaked softmaxes."""
+    rng = np.random.default_rng(seed)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        last = name.rsplit(".", 1)[-1]
+        if last in ("norm", "norm1", "norm2"):
+            a = rng.normal(1.0, 0.2, shape)
+        elif last == "sink":
+            a = rng.normal(0.5, 1.5, shape)
+        elif last == "correction":
+            a = rng.normal(0.0, 0.08, shape)
+        elif last == "b":
+            a = rng.normal(0.0, 0.3, shape)
+        elif name == "embed":
+            a = rng.normal(0.0, 1.0, shape)
+        else:
+            big = sharp if last in ("q", "k", "uq", "uk", "dkv", "g", "sg", "router") else 1.0
+            a = rng.normal(0.0, 1.0 / math.sqrt(shape[-1]), shape) * big
+        out[name] = to_bfloat16(a)
+    return out
