@@ -7,6 +7,7 @@
     python bench.py --family forisun [--size s|m] [--batch B] [--steps K]   # Forisun beside GPT-2 at equal size
     python bench.py --family lusalorn [--size s|m] [--batch B] [--steps K]  # Lusalorn beside GPT-2 at equal size
     python bench.py --family seledra [--size s|m] [--batch B] [--steps K]   # Seledra beside Lusalorn at equal size
+    python bench.py --family tibopel [--size s|m] [--batch B] [--steps K]   # Tibopel beside Forisun at equal size
 
 A "step" is one decode step of the whole batch.  The default run has the layer
 sizes of GPT-2 small (BASELINE.json's third configuration) with seeded random
@@ -539,6 +540,37 @@ def seledra_config(size):
     return ours, lusalorn_config(size)[0]
 
 
+TIBOPEL_SIZES = {
+    # width, attention (heads, kv heads, dim, vdim, chunk, rotated), latent attention (heads, dim, rot_dim, vdim,
+    # kv_rank, q_rank), experts (experts, identity, top, expert ff, shared ff), layer runs
+    "s": (1024, (8, 2, 128, 128, 512, 64), (8, 64, 32, 64, 256, 384), (16, 4, 4, 512, 1024), 4),
+    "m": (2048, (16, 4, 128, 128, 512, 64), (16, 128, 64, 128, 512, 768), (64, 8, 6, 1408, 2816), 4),
+}
+
+
+def tibopel_config(size):
+    """A Tibopel configuration with layer sizes of a real model's order (random weights): chunked grouped-query
+    attention and latent attention with sinks in turns, the second pair of layer runs with the tensors of the first,
+    every layer with routed experts (identity experts among them) and a gated shared expert; and beside it the
+    library's closest design, Forisun (latent attention over cached rows, routed experts), at the same size: equal
+    width, layer count, vocabulary, latent sizes and experts."""
+    D, (H, G, d, dv, chunk, rot), (lh, ld, lr, lv, r, rq), (E, n_id, top, ff, shared), L = TIBOPEL_SIZES[size]
+    att = {"heads": H, "kv_heads": G, "dim": d, "vdim": dv, "scale": d ** -0.5, "mask": {"size": chunk},
+           "rot": {"base": 1.0e6, "dims": rot, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 512}}}
+    lat = {"heads": lh, "dim": ld, "rot_dim": lr, "vdim": lv, "kv_rank": r, "q_rank": rq, "scale": (ld + lr) ** -0.5,
+           "rot": {"base": 10000.0, "dims": lr}}
+    mlp = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": E, "identity": n_id, "top": top}, "shared": {"ff": shared}}
+    layers = []
+    for i in range(L):
+        layer = {"type": "latent_attention" if i % 2 else "attention", "mixer": lat if i % 2 else att, "mlp": mlp}
+        if i >= 2:
+            layer["weights_of"] = i % 2
+        layers.append(layer)
+    ours = {"architecture": "Tibopel", "vocab": FAMILY_VOCAB, "width": D, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+            "layers": layers}
+    return ours, forisun_config(size)[0]
+
+
 def stage_times(model, prompts, single_steps=8):
     """Device milliseconds per stage of one eager prompt step and of eager single-token steps (their mean)."""
     import torch
@@ -562,15 +594,16 @@ def stage_times(model, prompts, single_steps=8):
 
 
 def run_family(args):
-    """``--family forisun | lusalorn | seledra``: prompt and single-token throughput of that design at sizes of a real
-    model's order beside GPT-2 (Seledra: beside Lusalorn) at equal size, the same workload shape as the default run (2 x 1,024-token prompts; a batch from
+    """``--family forisun | lusalorn | seledra | tibopel``: prompt and single-token throughput of that design at sizes of a real
+    model's order beside GPT-2 (Seledra: beside Lusalorn; Tibopel: beside Forisun) at equal size, the same workload shape as the default run (2 x 1,024-token prompts; a batch from
     512-token prompts towards 1,024).  Prints one JSON line; the default run and its line are not touched."""
     import numpy as np
     from math_utils_b200.sampling import SamplingParams
     pk = peaks()
     rng = np.random.default_rng(0)
-    configs = {"forisun": forisun_config, "lusalorn": lusalorn_config, "seledra": seledra_config}[args.family](args.size)
-    other = "lusalorn_twin" if args.family == "seledra" else "gpt2_twin"
+    configs = {"forisun": forisun_config, "lusalorn": lusalorn_config, "seledra": seledra_config,
+               "tibopel": tibopel_config}[args.family](args.size)
+    other = {"seledra": "lusalorn_twin", "tibopel": "forisun_twin"}.get(args.family, "gpt2_twin")
     record = {"family": args.family, "size": args.size, "batch": args.batch, "steps": args.steps, "dtype": "bfloat16",
               "data": "synthetic: random weights, random tokens", "peaks": pk, "models": {}}
     for name, cfg in zip((args.family, other), configs):
@@ -757,8 +790,9 @@ def main():
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN, help="with --only decode: tokens per prompt")
     ap.add_argument("--reference-dir", default="", help="with --impl reference: a checkout other than baseline/_ref")
     ap.add_argument("--tokens", type=int, default=0, help="with --config: fewer tokens per request than fill the context")
-    ap.add_argument("--family", default="", choices=["", "forisun", "lusalorn", "seledra"],
-                    help="that design at sizes of a real model's order beside GPT-2 (seledra: beside Lusalorn) at equal size")
+    ap.add_argument("--family", default="", choices=["", "forisun", "lusalorn", "seledra", "tibopel"],
+                    help="that design at sizes of a real model's order beside GPT-2 (seledra: beside Lusalorn; tibopel: "
+                         "beside Forisun) at equal size")
     ap.add_argument("--size", default="s", choices=sorted(FORISUN_SIZES), help="with --family: which sizes")
     args = ap.parse_args()
     if args.gpus != 1:
