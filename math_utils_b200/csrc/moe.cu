@@ -264,6 +264,63 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, long long ldy, c
     }
 }
 
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// The same for rows that are whole 16-byte pieces: four entries a thread, every row's piece asked for before the
+// first is used.  TOP > 0: the number of choices at compile time (the loads of all choices are in flight together).
+template <typename TX, int TOP>
+__global__ void moe_combine_vec_kernel(const float* __restrict__ y, long long ldy, const int* __restrict__ slot_of,
+                                       const float* __restrict__ weight_of, int top, int width, float* __restrict__ out,
+                                       long long ldo, const TX* __restrict__ x, long long ldx,
+                                       const float* __restrict__ shared, long long lds,
+                                       const float* __restrict__ shared_gate, int add) {
+    pdl_trigger();
+    pdl_wait();
+    const int t = blockIdx.x;
+    if (TOP > 0) top = TOP;
+    for (int d = 4 * threadIdx.x; d < width; d += 4 * blockDim.x) {
+        float4 v = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (TOP > 0) {
+            float4 row[TOP > 0 ? TOP : 1];
+            float w[TOP > 0 ? TOP : 1];
+#pragma unroll
+            for (int k = 0; k < TOP; ++k) {
+                const int slot = slot_of[(long long)t * TOP + k];
+                w[k] = weight_of[(long long)t * TOP + k];
+                row[k] = slot >= 0 ? load4(y + (long long)slot * ldy + d) : load4(x + (long long)t * ldx + d);
+            }
+#pragma unroll
+            for (int k = 0; k < TOP; ++k) {                                // in the order of the choices
+                v.x += w[k] * row[k].x; v.y += w[k] * row[k].y; v.z += w[k] * row[k].z; v.w += w[k] * row[k].w;
+            }
+        } else {
+            for (int k = 0; k < top; ++k) {
+                const int slot = slot_of[(long long)t * top + k];
+                const float w = weight_of[(long long)t * top + k];
+                const float4 row = slot >= 0 ? load4(y + (long long)slot * ldy + d) : load4(x + (long long)t * ldx + d);
+                v.x += w * row.x; v.y += w * row.y; v.z += w * row.z; v.w += w * row.w;
+            }
+        }
+        if (shared) {
+            const float g = shared_gate ? shared_gate[t] : 1.0f;
+            const float4 sh = load4(shared + (long long)t * lds + d);
+            v.x += g * sh.x; v.y += g * sh.y; v.z += g * sh.z; v.w += g * sh.w;
+        }
+        float* dst = out + (long long)t * ldo + d;
+        if (add) {
+            const float4 old = load4(dst);
+            v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+        }
+        *reinterpret_cast<float4*>(dst) = v;
+    }
+}
+
 // The same sum, normed and added into the residual stream: out[t, :] += tanh(alpha v) w + b with v the token's sum.
 __global__ void moe_combine_tanh_kernel(const float* __restrict__ y, long long ldy, const int* __restrict__ slot_of,
                                         const float* __restrict__ weight_of, int top, int width,
@@ -364,6 +421,28 @@ MU_EXPORT int mu_moe_combine(const float* y, long long ldy, const int* slot_of, 
     if (n_tokens <= 0) return MU_OK;
     if (!y || !slot_of || !weight_of || !out || top <= 0 || width <= 0) return MU_ERR_BAD_ARGUMENT;
     const dim3 grid(n_tokens), block(width >= 1024 ? 256 : 128);
+    const bool vec = width % 4 == 0 && ldy % 4 == 0 && ldo % 4 == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)out & 15) == 0 &&
+                     (!x || (ldx % 4 == 0 && ((uintptr_t)x & (x_bf16 ? 7 : 15)) == 0)) &&
+                     (!shared || (lds % 4 == 0 && ((uintptr_t)shared & 15) == 0));
+    if (vec) {
+        const dim3 vblock(width >= 1024 ? 256 : width >= 512 ? 128 : 64);
+#define MU_COMBINE(TX, TOP)                                                                                            \
+    return mu::launch_pdl(mu::moe_combine_vec_kernel<TX, TOP>, grid, vblock, 0, (cudaStream_t)stream, 1, y, ldy, slot_of, \
+                          weight_of, top, width, out, ldo, (const TX*)x, ldx, shared, lds, shared_gate, add)
+        if (x_bf16) {
+            if (top == 2) MU_COMBINE(__nv_bfloat16, 2);
+            if (top == 4) MU_COMBINE(__nv_bfloat16, 4);
+            if (top == 6) MU_COMBINE(__nv_bfloat16, 6);
+            if (top == 8) MU_COMBINE(__nv_bfloat16, 8);
+            MU_COMBINE(__nv_bfloat16, 0);
+        }
+        if (top == 2) MU_COMBINE(float, 2);
+        if (top == 4) MU_COMBINE(float, 4);
+        if (top == 6) MU_COMBINE(float, 6);
+        if (top == 8) MU_COMBINE(float, 8);
+        MU_COMBINE(float, 0);
+#undef MU_COMBINE
+    }
     if (x_bf16)
         return mu::launch_pdl(mu::moe_combine_kernel<__nv_bfloat16>, grid, block, 0, (cudaStream_t)stream, 1, y, ldy,
                               slot_of, weight_of, top, width, out, ldo, (const __nv_bfloat16*)x, ldx, shared, lds,

@@ -172,7 +172,9 @@ def routed_experts(h, w, p, f):
 def layer_forward(x, w, config, i):
     """x + mixer(norm1 x) + ff(norm2 x), both sublayers reading the same x."""
     layer = config["layers"][i]
-    j = int(layer.get("weights_of", i))
+    j = i
+    while config["layers"][j].get("weights_of") is not None:                    # whose tensors: the owner's
+        j = int(config["layers"][j]["weights_of"])
     p = f"l{j}."
     eps = float(config["norm"]["eps"])
     h1 = rms_norm(x, w[p + "norm1"], eps)
