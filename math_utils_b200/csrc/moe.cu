@@ -5,7 +5,7 @@
 //
 // mu_moe_route    z = W_r h in float32; s = sigmoid(z) (or softmax over the experts); the `top` experts with
 //                 the largest s + correction are chosen (ties: the lower index); weight = s * scale
-//                 (optionally divided by the chosen experts' sum).  One block per token.
+//                 (optionally divided by the chosen experts' sum).  A block per token, or per eight in prompt steps.
 // mu_moe_group    counts the pairs of each expert, gives every pair a slot so that an expert's slots are
 //                 contiguous, and lists tiles of TM slots that never straddle two experts.
 // mu_moe_gemm     for every tile: out[slot, :] = act(W1[e] x[row]) (* W2[e] x[row]) on CUDA cores, one running
@@ -30,53 +30,77 @@ constexpr int MOE_TM = 32, MOE_TN = 64, MOE_TK = 32;
 
 constexpr int ROUTE_WARPS = 16;
 
-// One block per token: the token's row is staged in shared memory as float32, the warps share the experts (each
-// logit one warp's sum over the row, lanes striding along it), then the first warp scores and chooses.
-template <typename T>
+// A block takes TOK consecutive tokens: their rows are staged in shared memory as float32, the warps share the
+// experts (each logit one warp's sum over the row, lanes striding along it; a router row is read once for the
+// block's tokens), then warp i scores and chooses for token i.  A token's sums run in the same order whatever TOK
+// is and whichever tokens share its block.
+template <typename T, int TOK>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ router,
                  const float* __restrict__ correction, int n_tokens, int hidden, int n_experts, int top,
                  float scale, int softmax, int renormalize, int* __restrict__ expert_of,
                  float* __restrict__ weight_of, float renorm_eps, const float* __restrict__ gate_w,
                  float* __restrict__ gate_out) {
-    extern __shared__ __align__(16) float sm[];        // row [hidden], scores [n_experts], choice [n_experts]
+    extern __shared__ __align__(16) float sm[];        // rows [TOK][hidden], scores [TOK][n_experts], choice [TOK][n_experts]
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x;
+    const int t0 = blockIdx.x * TOK, nt = min(TOK, n_tokens - t0);
     float* hrow = sm;
-    float* score = sm + hidden;
-    float* choice = score + n_experts;
-    const T* row = h + (long long)t * ldh;
-    for (int d = threadIdx.x; d < hidden; d += blockDim.x) hrow[d] = to_float(row[d]);
+    float* score_all = sm + (size_t)TOK * hidden;
+    float* choice_all = score_all + TOK * n_experts;
+    for (int i = 0; i < TOK; ++i) {
+        const T* row = h + (long long)(t0 + i) * ldh;
+        for (int d = threadIdx.x; d < hidden; d += blockDim.x) hrow[i * hidden + d] = i < nt ? to_float(row[d]) : 0.0f;
+    }
     __syncthreads();
     const bool wide = hidden % 4 == 0 && ((uintptr_t)router & 15) == 0 &&
                       ((uintptr_t)gate_w & 15) == 0;                          // rows of the router in 16-byte pieces
     // (with gate_w: one more sum, over the shared expert's gate row, by the warp whose turn it is)
     for (int e = warp; e < n_experts + (gate_w ? 1 : 0); e += ROUTE_WARPS) {
         const float* w = e < n_experts ? router + (long long)e * hidden : gate_w;
-        float z = 0.0f;
+        float z[TOK];
         if (wide) {
             const float4* w4 = reinterpret_cast<const float4*>(w);
             const float4* h4 = reinterpret_cast<const float4*>(hrow);
-            float z0 = 0.0f, z1 = 0.0f, z2 = 0.0f, z3 = 0.0f;             // the lane's sum in four parts, then in order
-#pragma unroll 4
-            for (int d = lane; d < hidden / 4; d += 32) {
-                const float4 a = h4[d], b = w4[d];
-                z0 += a.x * b.x; z1 += a.y * b.y; z2 += a.z * b.z; z3 += a.w * b.w;
+            const int n4 = hidden / 4;
+            float z0[TOK], z1[TOK], z2[TOK], z3[TOK];                        // a lane's sum in four parts, then in order
+#pragma unroll
+            for (int i = 0; i < TOK; ++i) z0[i] = z1[i] = z2[i] = z3[i] = 0.0f;
+#pragma unroll 2
+            for (int d = lane; d < n4; d += 32) {
+                const float4 b = w4[d];
+#pragma unroll
+                for (int i = 0; i < TOK; ++i) {
+                    const float4 a = h4[i * n4 + d];
+                    z0[i] += a.x * b.x; z1[i] += a.y * b.y; z2[i] += a.z * b.z; z3[i] += a.w * b.w;
+                }
             }
-            z = (z0 + z1) + (z2 + z3);
+#pragma unroll
+            for (int i = 0; i < TOK; ++i) z[i] = (z0[i] + z1[i]) + (z2[i] + z3[i]);
         } else {
-            for (int d = lane; d < hidden; d += 32) z += hrow[d] * w[d];
+#pragma unroll
+            for (int i = 0; i < TOK; ++i) z[i] = 0.0f;
+            for (int d = lane; d < hidden; d += 32) {
+                const float b = w[d];
+#pragma unroll
+                for (int i = 0; i < TOK; ++i) z[i] += hrow[i * hidden + d] * b;
+            }
         }
-        z = warp_sum(z);
-        if (lane == 0) {
-            if (e < n_experts) score[e] = z;
-            else gate_out[t] = 1.0f / (1.0f + expf(-z));
+#pragma unroll
+        for (int i = 0; i < TOK; ++i) {
+            const float zi = warp_sum(z[i]);
+            if (lane == 0 && i < nt) {
+                if (e < n_experts) score_all[i * n_experts + e] = zi;
+                else gate_out[t0 + i] = 1.0f / (1.0f + expf(-zi));
+            }
         }
     }
     __syncthreads();
-    if (warp != 0) return;
+    if (warp >= nt) return;
+    const int t = t0 + warp;
+    float* score = score_all + warp * n_experts;
+    float* choice = choice_all + warp * n_experts;
     if (softmax) {
         float top_z = -INFINITY, sum = 0.0f;
         for (int e = lane; e < n_experts; e += 32) top_z = fmaxf(top_z, score[e]);
@@ -359,17 +383,29 @@ MU_EXPORT int mu_moe_route(const void* h, long long ldh, int h_bf16, const float
     if (!h || !router || !expert_of || !weight_of || hidden <= 0 || n_experts <= 0 || top <= 0 || top > n_experts ||
         (gate_w != nullptr) != (gate_out != nullptr))
         return MU_ERR_BAD_ARGUMENT;
-    const size_t smem = (size_t)(hidden + 2 * n_experts) * sizeof(float);
+    // prompt steps: several tokens a block, so that the router's rows are read once for all of them (with a block a
+    // token the router came out of the L2 once per token); few tokens: a block each, spread over the SMs
+    int tok = n_tokens >= 4 * mu::sm_count() ? 8 : 1;
+    while (tok > 1 && (size_t)tok * (hidden + 2 * n_experts) * sizeof(float) > 48 * 1024) tok /= 2;
+    const size_t smem = (size_t)tok * (hidden + 2 * n_experts) * sizeof(float);
     if (smem > 48 * 1024) return MU_ERR_UNSUPPORTED_SIZE;
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(n_tokens), block(mu::ROUTE_WARPS * 32);
-    if (h_bf16)
-        return mu::launch_pdl(mu::moe_route_kernel<__nv_bfloat16>, grid, block, smem, s, 1, (const __nv_bfloat16*)h, ldh,
-                              router, correction, n_tokens, hidden, n_experts, top, scale, softmax, renormalize,
-                              expert_of, weight_of, renorm_eps, gate_w, gate_out);
-    return mu::launch_pdl(mu::moe_route_kernel<float>, grid, block, smem, s, 1, (const float*)h, ldh, router, correction,
-                          n_tokens, hidden, n_experts, top, scale, softmax, renormalize, expert_of, weight_of, renorm_eps,
-                          gate_w, gate_out);
+    const dim3 grid((n_tokens + tok - 1) / tok), block(mu::ROUTE_WARPS * 32);
+#define MU_ROUTE(T, TOK)                                                                                               \
+    return mu::launch_pdl(mu::moe_route_kernel<T, TOK>, grid, block, smem, s, 1, (const T*)h, ldh, router, correction, \
+                          n_tokens, hidden, n_experts, top, scale, softmax, renormalize, expert_of, weight_of,         \
+                          renorm_eps, gate_w, gate_out)
+    if (h_bf16) {
+        if (tok == 8) MU_ROUTE(__nv_bfloat16, 8);
+        if (tok == 4) MU_ROUTE(__nv_bfloat16, 4);
+        if (tok == 2) MU_ROUTE(__nv_bfloat16, 2);
+        MU_ROUTE(__nv_bfloat16, 1);
+    }
+    if (tok == 8) MU_ROUTE(float, 8);
+    if (tok == 4) MU_ROUTE(float, 4);
+    if (tok == 2) MU_ROUTE(float, 2);
+    MU_ROUTE(float, 1);
+#undef MU_ROUTE
 }
 
 // tile_info needs 3 * (n_pairs / tile_rows + n_experts) ints.  tile_rows: the CUDA-core product takes tiles of
