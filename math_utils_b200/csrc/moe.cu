@@ -49,9 +49,25 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
     float* hrow = sm;
     float* score_all = sm + (size_t)TOK * hidden;
     float* choice_all = score_all + TOK * n_experts;
-    for (int i = 0; i < TOK; ++i) {
-        const T* row = h + (long long)(t0 + i) * ldh;
-        for (int d = threadIdx.x; d < hidden; d += blockDim.x) hrow[i * hidden + d] = i < nt ? to_float(row[d]) : 0.0f;
+    if (sizeof(T) == 2 && hidden % 8 == 0 && ldh % 8 == 0 && ((uintptr_t)h & 15) == 0) {
+        // eight bfloat16 entries a thread and load
+        const int pieces = hidden / 8;
+        for (int j = threadIdx.x; j < TOK * pieces; j += blockDim.x) {
+            const int i = j / pieces, c = j % pieces;
+            uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+            if (i < nt) raw = *reinterpret_cast<const uint4*>(h + (long long)(t0 + i) * ldh + 8 * c);
+            const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float4* dst = reinterpret_cast<float4*>(hrow + i * hidden + 8 * c);
+            const float2 a = __bfloat1622float2(p2[0]), b = __bfloat1622float2(p2[1]);
+            const float2 c2 = __bfloat1622float2(p2[2]), d2 = __bfloat1622float2(p2[3]);
+            dst[0] = make_float4(a.x, a.y, b.x, b.y);
+            dst[1] = make_float4(c2.x, c2.y, d2.x, d2.y);
+        }
+    } else {
+        for (int i = 0; i < TOK; ++i) {
+            const T* row = h + (long long)(t0 + i) * ldh;
+            for (int d = threadIdx.x; d < hidden; d += blockDim.x) hrow[i * hidden + d] = i < nt ? to_float(row[d]) : 0.0f;
+        }
     }
     __syncthreads();
     const bool wide = hidden % 4 == 0 && ((uintptr_t)router & 15) == 0 &&
@@ -67,8 +83,8 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
             float z0[TOK], z1[TOK], z2[TOK], z3[TOK];                        // a lane's sum in four parts, then in order
 #pragma unroll
             for (int i = 0; i < TOK; ++i) z0[i] = z1[i] = z2[i] = z3[i] = 0.0f;
-#pragma unroll 2
-            for (int d = lane; d < n4; d += 32) {
+#pragma unroll 8
+            for (int d = lane; d < n4; d += 32) {                            // (unrolled: the row's loads go out together)
                 const float4 b = w4[d];
 #pragma unroll
                 for (int i = 0; i < TOK; ++i) {
