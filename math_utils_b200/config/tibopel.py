@@ -89,8 +89,14 @@ class TibopelConfig:
         src = layer.get("weights_of")
         if src is not None:
             src = lr.integer("weights_of", minimum=0)
-            if src >= i:
-                raise ConfigError(f"{where}: weights_of {src} must name an earlier layer")
+            seen = {i}
+            while True:                                    # up to the layer that owns the tensors
+                if src >= len(layers) or src in seen or not isinstance(layers[src], Mapping):
+                    raise ConfigError(f"{where}: weights_of leads to no layer that has tensors of its own")
+                if layers[src].get("weights_of") is None:
+                    break
+                seen.add(src)
+                src = KeyReader(layers[src], f"config.json: layers[{src}]").integer("weights_of", minimum=0)
             if layers[src].get("type") != kind:
                 raise ConfigError(f"{where}: a layer that uses layer {src}'s tensors has its type")
         m = _sub(lr, "mixer")
@@ -162,7 +168,7 @@ class TibopelConfig:
             {"hidden_size": D, "n_heads": int(m["heads"]), "dim": int(m["dim"]), "rot_dim": int(m["rot_dim"]),
              "vdim": int(m["vdim"]), "kv_rank": int(m["kv_rank"]), "q_rank": int(m["q_rank"]),
              "softmax_scale": float(m["scale"]), "eps": self.norm_eps, "rot": m["rot"], "gate": False, "sink": True,
-             "rot_layout": "pairs"},
+             "rot_layout": "pairs", "exact_weights": True},
             {"dq": x + "dq", "dq_norm": x + "dq.norm", "uq": x + "uq", "dkv": x + "dkv", "dkv_norm": x + "dkv.norm",
              "uk": x + "uk", "uv": x + "uv", "sink": x + "sink", "out": x + "o"})
 
@@ -181,11 +187,7 @@ class TibopelConfig:
         D = self.width
         layers, schedule, own, ignored = [], [], {}, []
         for i, layer in enumerate(self.layers):
-            src = layer.get("weights_of")
-            if src is not None:
-                # that layer's parts (or, if it borrows its tensors too, the ones it uses), a cache of its own
-                own[i] = own[int(src)]
-                schedule.append(ScheduleEntry(layer=own[i], cache_of=i))
+            if layer.get("weights_of") is not None:
                 continue
             p = f"l{i}."
             mlp = layer.get("mlp")
@@ -196,7 +198,13 @@ class TibopelConfig:
                 norm2, ffn = self._norm(p + "norm2"), self._mlp(mlp, p)
             own[i] = len(layers)
             layers.append(LayerSpec("parallel_pre_norm", self._norm(p + "norm1"), self._mixer(layer, p), norm2, ffn))
-            schedule.append(ScheduleEntry(layer=own[i], cache_of=i))
+        for i, layer in enumerate(self.layers):
+            # a layer with `weights_of` runs that layer's parts (or, if that one borrows its tensors too, the ones
+            # it uses) with a cache of its own
+            j = i
+            while self.layers[j].get("weights_of") is not None:
+                j = int(self.layers[j]["weights_of"])
+            schedule.append(ScheduleEntry(layer=own[j], cache_of=i))
         plan = ModelPlan(
             architecture=self.architecture, vocab_size=self.vocab, hidden_size=D, max_positions=self.max_positions,
             embedding=PartSpec("token_embedding", {"vocab_size": self.vocab, "hidden_size": D}, {"weight": "embed"}),

@@ -10,6 +10,10 @@
 // worked on.  Softmax state and O stay in float32 registers.  With n_splits > 1 (single-token steps) a block takes a
 // share of the pages and leaves an unnormalised partial result for the merge kernel.
 //
+// TWO (an option for designs that want the softmax's weights at 32 bits): P enters the second product as two bfloat16
+// terms, the rounded weight and what the rounding left (some 16 bits of mantissa instead of 8), and the row sums are
+// those of the unrounded weights.
+//
 // Sizes taken: width a multiple of 16, kv_rank = 32 * NT with NT in {2, 4, 8, 12, 16}, pages of 64 positions.
 #include "common.cuh"
 
@@ -44,7 +48,7 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 
 // tiles: int32 [n][2] = (first flat token, count <= 64) of runs of tokens of one sequence, or null: token t alone.
 // grid: (tiles * sub-tiles, n_splits, head chunks).
-template <int NT>
+template <int NT, bool TWO>
 __global__ void __launch_bounds__(LM_THREADS)
 latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __restrict__ rows,
                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ tok_pos,
@@ -57,7 +61,8 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
     __nv_bfloat16* Ks = reinterpret_cast<__nv_bfloat16*>(lm_raw);            // [2][64][w8]
     __nv_bfloat16* Qs = Ks + 2 * LM_KEYS * w8;                               // [32][w8]
     __nv_bfloat16* Ps = Qs + LM_ROWS * w8;                                   // [32][72]
-    float* red_max = reinterpret_cast<float*>(Ps + LM_ROWS * 72);            // [4][32]
+    __nv_bfloat16* Pl = Ps + LM_ROWS * 72;                                   // [32][72]: what rounding P left (TWO)
+    float* red_max = reinterpret_cast<float*>(Pl + LM_ROWS * 72);            // [4][32]
     float* red_sum = red_max + 4 * LM_ROWS;                                  // [4][32]
     int* row_pos = reinterpret_cast<int*>(red_sum + 4 * LM_ROWS);            // [32]
     int* row_src = row_pos + LM_ROWS;                                        // [32] token * n_heads + head, or -1
@@ -174,10 +179,19 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
             const float p0 = new_a == -INFINITY ? 0.0f : expf(s[j][0] - new_a), p1 = new_a == -INFINITY ? 0.0f : expf(s[j][1] - new_a);
             const float p2 = new_b == -INFINITY ? 0.0f : expf(s[j][2] - new_b), p3 = new_b == -INFINITY ? 0.0f : expf(s[j][3] - new_b);
             const __nv_bfloat162 pa = __floats2bfloat162_rn(p0, p1), pb = __floats2bfloat162_rn(p2, p3);
-            // the sums use what the second product will see: the rounded weights
-            sum_a += __low2float(pa) + __high2float(pa);
-            sum_b += __low2float(pb) + __high2float(pb);
             const int col = g * 16 + j * 8 + 2 * t4;
+            if (TWO) {
+                sum_a += p0 + p1;
+                sum_b += p2 + p3;
+                *reinterpret_cast<__nv_bfloat162*>(Pl + ra * 72 + col) =
+                    __floats2bfloat162_rn(p0 - __low2float(pa), p1 - __high2float(pa));
+                *reinterpret_cast<__nv_bfloat162*>(Pl + rb * 72 + col) =
+                    __floats2bfloat162_rn(p2 - __low2float(pb), p3 - __high2float(pb));
+            } else {
+                // the sums use what the second product will see: the rounded weights
+                sum_a += __low2float(pa) + __high2float(pa);
+                sum_b += __low2float(pb) + __high2float(pb);
+            }
             *reinterpret_cast<__nv_bfloat162*>(Ps + ra * 72 + col) = pa;
             *reinterpret_cast<__nv_bfloat162*>(Ps + rb * 72 + col) = pb;
         }
@@ -203,12 +217,23 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
         for (int k0 = 0; k0 < LM_KEYS; k0 += 16) {
             const uint32_t a0 = *reinterpret_cast<const uint32_t*>(pa_ptr + k0), a1 = *reinterpret_cast<const uint32_t*>(pb_ptr + k0);
             const uint32_t a2 = *reinterpret_cast<const uint32_t*>(pa_ptr + k0 + 8), a3 = *reinterpret_cast<const uint32_t*>(pb_ptr + k0 + 8);
+            uint32_t l0 = 0u, l1 = 0u, l2 = 0u, l3 = 0u;
+            if (TWO) {
+                const __nv_bfloat16* la = Pl + ra * 72 + 2 * t4 + k0;
+                const __nv_bfloat16* lb = Pl + rb * 72 + 2 * t4 + k0;
+                l0 = *reinterpret_cast<const uint32_t*>(la), l1 = *reinterpret_cast<const uint32_t*>(lb);
+                l2 = *reinterpret_cast<const uint32_t*>(la + 8), l3 = *reinterpret_cast<const uint32_t*>(lb + 8);
+            }
 #pragma unroll
             for (int i = 0; i < NT; i += 2) {
                 uint32_t b[4];
                 ldmatrix_x4_trans(b, vbase + k0 * w8 + i * 8);
                 mma_bf16(o_acc[i], a0, a1, a2, a3, b[0], b[1]);
                 mma_bf16(o_acc[i + 1], a0, a1, a2, a3, b[2], b[3]);
+                if (TWO) {
+                    mma_bf16(o_acc[i], l0, l1, l2, l3, b[0], b[1]);
+                    mma_bf16(o_acc[i + 1], l0, l1, l2, l3, b[2], b[3]);
+                }
             }
         }
         __syncthreads();
@@ -255,21 +280,21 @@ latent_attention_mma_kernel(const float* __restrict__ q, const __nv_bfloat16* __
 }
 
 inline size_t lm_smem(int width) {
-    return (size_t)(2 * LM_KEYS + LM_ROWS) * (width + 8) * 2 + LM_ROWS * 72 * 2 + 2 * 4 * LM_ROWS * 4 + 2 * LM_ROWS * 4;
+    return (size_t)(2 * LM_KEYS + LM_ROWS) * (width + 8) * 2 + 2 * LM_ROWS * 72 * 2 + 2 * 4 * LM_ROWS * 4 + 2 * LM_ROWS * 4;
 }
 
-template <int NT>
+template <int NT, bool TWO>
 int launch_lm(dim3 grid, size_t smem, cudaStream_t s, const float* q, const __nv_bfloat16* rows, const int* block_table,
               int max_pages, const int* tok_pos, const int* tok_seq, const int* tiles, int n_heads, int width, float scale,
               int n_splits, __nv_bfloat16* out, long long ldo, float* part_o, float* part_ml, const float* sink) {
     static bool set = false;
     if (!set) {
-        if (cudaFuncSetAttribute(latent_attention_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+        if (cudaFuncSetAttribute(latent_attention_mma_kernel<NT, TWO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
             cudaSuccess)
             return MU_ERR_LAUNCH;
         set = true;
     }
-    return launch_pdl(latent_attention_mma_kernel<NT>, grid, dim3(LM_THREADS), smem, s, 1, q, rows, block_table, max_pages,
+    return launch_pdl(latent_attention_mma_kernel<NT, TWO>, grid, dim3(LM_THREADS), smem, s, 1, q, rows, block_table, max_pages,
                       tok_pos, tok_seq, tiles, n_heads, width, scale, n_splits, out, ldo, part_o, part_ml,
                       n_splits == 1 ? sink : nullptr);
 }
@@ -286,11 +311,13 @@ MU_EXPORT int mu_latent_attention_mma_fits(int kv_rank, int width, int page_toke
 // q float32 [n_tokens][n_heads][width]; out bfloat16 [n_tokens][ldo], head h at columns h * kv_rank.
 // tiles (n_tiles of them) for steps with several tokens a sequence; null: every token is a sequence's one token.
 // With n_splits > 1 the partial results go to part_o / part_ml, for mu_latent_merge.  sink (one float per head, or
-// null): exp(sink[h]) joins head h's softmax denominator; with splits it is the merge that adds it.
+// null): exp(sink[h]) joins head h's softmax denominator; with splits it is the merge that adds it.  two_term: the
+// softmax's weights enter the second product as two bfloat16 terms.
 MU_EXPORT int mu_latent_attention_mma(const float* q, const void* rows, const int* block_table, int max_pages,
                                       const int* tok_pos, const int* tok_seq, const int* tiles, int n_tiles, int n_tokens,
                                       int n_heads, int kv_rank, int width, float scale, int n_splits, void* out,
-                                      long long ldo, float* part_o, float* part_ml, void* stream, const float* sink) {
+                                      long long ldo, float* part_o, float* part_ml, void* stream, const float* sink,
+                                      int two_term) {
     if (n_tokens <= 0) return MU_OK;
     if (!q || !rows || !block_table || !tok_pos || !tok_seq || !out || n_heads <= 0 || n_splits < 1 || n_splits > 65535 ||
         (n_splits > 1 && (!part_o || !part_ml || tiles)) || (tiles && n_tiles <= 0) || (ldo & 1))
@@ -305,8 +332,11 @@ MU_EXPORT int mu_latent_attention_mma(const float* q, const void* rows, const in
     typedef __nv_bfloat16 bf;
 #define MU_LM(N)                                                                                                       \
     case N:                                                                                                            \
-        return mu::launch_lm<N>(grid, smem, s, q, (const bf*)rows, block_table, max_pages, tok_pos, tok_seq, tiles,    \
-                                n_heads, width, scale, n_splits, (bf*)out, ldo, part_o, part_ml, sink);
+        if (two_term)                                                                                                  \
+            return mu::launch_lm<N, true>(grid, smem, s, q, (const bf*)rows, block_table, max_pages, tok_pos, tok_seq, \
+                                          tiles, n_heads, width, scale, n_splits, (bf*)out, ldo, part_o, part_ml, sink); \
+        return mu::launch_lm<N, false>(grid, smem, s, q, (const bf*)rows, block_table, max_pages, tok_pos, tok_seq,    \
+                                       tiles, n_heads, width, scale, n_splits, (bf*)out, ldo, part_o, part_ml, sink);
     switch (kv_rank / 32) { MU_LM(2) MU_LM(4) MU_LM(8) MU_LM(12) MU_LM(16) }
 #undef MU_LM
     return MU_ERR_UNSUPPORTED_SIZE;

@@ -133,7 +133,7 @@ _SIGNATURES = {
     "mu_latent_merge": [_c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_p, _c_ll, _c_int, _c_p, _c_p],
     "mu_latent_attention_mma_fits": [_c_int, _c_int, _c_int],
     "mu_latent_attention_mma": [_c_p, _c_p, _c_p, _c_int, _c_p, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f,
-                                _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p],
+                                _c_int, _c_p, _c_ll, _c_p, _c_p, _c_p, _c_p, _c_int],
     "mu_moe_route": [_c_p, _c_ll, _c_int, _c_p, _c_p, _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_p, _c_p,
                      _c_p, _c_f, _c_p, _c_p],
     "mu_moe_group": [_c_p, _c_int, _c_int, _c_p, _c_p, _c_p, _c_p, _c_int, _c_p, _c_int],
@@ -792,7 +792,8 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
                      n_heads: int, kv_rank: int, scale: float, out: torch.Tensor, n_splits: int = 1,
                      part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
                      tiles: Optional[torch.Tensor] = None, single_tokens: bool = False,
-                     tensor_cores: Optional[bool] = None, sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     tensor_cores: Optional[bool] = None, sink: Optional[torch.Tensor] = None,
+                     two_term_weights: bool = False) -> torch.Tensor:
     """Attention of float32 queries [T, n_heads, width] over the latent rows 0..position of each token's sequence;
     ``out`` [T, n_heads * kv_rank] receives the weighted sums of the rows' first ``kv_rank`` values.
 
@@ -800,7 +801,9 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
     tokens group: ``tiles`` (int32 [n, 2]: first flat token and count <= 64 of runs of tokens of one sequence) or
     ``single_tokens`` (every token is the one token of its sequence); ``tensor_cores`` false keeps the CUDA-core
     kernel.  ``n_splits`` > 1 (single-token steps) cuts each sequence's rows into parts that are merged afterwards.
-    ``sink`` (float32, one per head): exp(sink[h]) is added to head h's softmax denominator, with no value behind it."""
+    ``sink`` (float32, one per head): exp(sink[h]) is added to head h's softmax denominator, with no value behind it.
+    ``two_term_weights``: on the tensor cores the softmax's weights enter the second product as two bfloat16 terms
+    (the rounded weight and what the rounding left), so that they act with some 16 bits instead of 8."""
     _need_cuda(q, rows, block_table, tok_pos, tok_seq, out, part_o, part_ml, tiles, sink)
     if sink is not None and (sink.dtype != torch.float32 or sink.numel() != n_heads or not sink.is_contiguous()):
         raise KernelError("latent_attention: the sink is one contiguous float32 per head")
@@ -828,7 +831,8 @@ def latent_attention(q: torch.Tensor, rows: torch.Tensor, block_table: torch.Ten
         _check(library().mu_latent_attention_mma(
             _ptr(q), _ptr(rows), _ptr(block_table), block_table.shape[1], _ptr(tok_pos), _ptr(tok_seq), _ptr(tiles),
             tiles.shape[0] if tiles is not None else 0, n_tokens, int(n_heads), int(kv_rank), int(width), float(scale),
-            int(n_splits), _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _stream(), _ptr(sink)), what)
+            int(n_splits), _ptr(out), out.stride(0), _ptr(part_o), _ptr(part_ml), _stream(), _ptr(sink),
+            int(two_term_weights)), what)
         if n_splits > 1:
             _check(library().mu_latent_merge(_ptr(part_o), _ptr(part_ml), n_tokens, int(n_heads), int(kv_rank),
                                              int(n_splits), _ptr(out), out.stride(0), 1, _stream(), _ptr(sink)), what)

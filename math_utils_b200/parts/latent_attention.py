@@ -18,7 +18,8 @@ their own, q = U_q rmsnorm(D_q h) (tensors ``dq`` [r_q, hidden], ``dq_norm`` [r_
 r_q] instead of ``q``; the norm's eps is ``eps``); ``gate`` false leaves the output gate out (no ``gate`` tensor);
 ``sink`` adds exp(s_h) to head h's softmax denominator, s a learned number per head (tensor ``sink`` [heads]) that
 is not scaled and has no value behind it; ``rot_layout`` ``"pairs"`` turns entry 2i with entry 2i + 1 instead of
-entry i with entry i + dims/2.
+entry i with entry i + dims/2; ``exact_weights`` keeps the softmax's weights at some 16 bits where the tensor-core
+kernel multiplies them with the latents (two bfloat16 terms a weight), for designs that want them at 32 bits.
 """
 from __future__ import annotations
 
@@ -43,6 +44,7 @@ class LatentAttention(Mixer):
         self.window = int(p("window", 0))
         self.q_rank = int(p("q_rank", 0))
         self.has_gate, self.has_sink = bool(p("gate", True)), bool(p("sink", False))
+        self.exact_weights = bool(p("exact_weights", False))
         self.rot_layout = p("rot_layout", "half")
         if self.rot_layout not in ("half", "pairs"):
             raise ConfigError(f"latent_attention: rot_layout '{self.rot_layout}' is not 'half' or 'pairs'")
@@ -140,7 +142,7 @@ class LatentAttention(Mixer):
         n_splits, part_o, part_ml = self.splits(ctx)
         ops.latent_attention(qa, cache.pages, table, cache.page_tokens, ctx.tok_pos, ctx.tok_seq, H, r, self.scale,
                              mixed, n_splits, part_o, part_ml, tiles=ctx.q_tiles, single_tokens=ctx.is_decode,
-                             sink=self.sink)
+                             sink=self.sink, two_term_weights=self.exact_weights)
         ctx.note("mixed", mixed)
         heads = ctx.buffer("latent.heads", (T, H * self.vdim), dt)
         ops.heads_gemm(mixed, self.v_up, heads, r, self.vdim, gate=gate)

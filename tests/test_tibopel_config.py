@@ -45,6 +45,16 @@ def test_configuration_and_plan():
     assert names == plain.tensor_shapes(CFG)
 
 
+def test_tensors_borrowed_from_a_later_layer():
+    cfg = json.loads(json.dumps(CFG))
+    cfg["layers"][0]["weights_of"] = 4                     # 0 -> 4 -> 2: layer 2 owns the tensors
+    cfg["layers"][2].pop("weights_of")
+    plan = TibopelConfig.from_json(cfg).plan()
+    assert [(e.layer, e.cache_of) for e in plan.schedule] == [(1, 0), (0, 1), (1, 2), (0, 3), (1, 4)]
+    names = {s.name for s in collect_tensor_specs(plan)}
+    assert "l2.mix.q" in names and "l0.mix.q" not in names and names == set(plain.tensor_shapes(cfg))
+
+
 def test_optional_keys():
     cfg = json.loads(json.dumps(CFG))
     del cfg["logit_softcap"]
@@ -71,7 +81,9 @@ def test_optional_keys():
     (lambda c: c["layers"][0].update(type="delta"), "type"),
     (lambda c: c["layers"][0]["mlp"].update(kind="dense"), "kind"),
     (lambda c: c["layers"][0]["mlp"]["router"].update(top=6), "top"),
-    (lambda c: c["layers"][2].update(weights_of=3), "weights_of"),
+    (lambda c: c["layers"][2].update(weights_of=2), "weights_of"),
+    (lambda c: c["layers"][2].update(weights_of=9), "weights_of"),
+    (lambda c: (c["layers"][0].update(weights_of=2), c["layers"][2].update(weights_of=0)), "weights_of"),
     (lambda c: c["layers"][3].update(weights_of=0), "type"),
     (lambda c: c["norm"].pop("eps"), "eps"),
     (lambda c: c.pop("width"), "width"),
