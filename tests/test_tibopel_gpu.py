@@ -413,7 +413,7 @@ def _chunk_heads(q, rows, pos, dim, vdim, H, G, scale, gate, chunk):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,dim,vdim,chunk", [(4, 2, 16, 24, 48), (3, 3, 6, 5, 7), (6, 1, 5, 15, 1), (4, 2, 64, 32, 64),
-                                                (2, 2, 8, 200, 160), (8, 2, 32, 64, 1000)])
+                                                (2, 2, 8, 200, 160), (8, 2, 32, 64, 1000), (34, 2, 16, 16, 48)])
 def test_chunked_attention_with_gates(dtype, H, G, dim, vdim, chunk):
     """The general kernel and the one of single-token steps.  In the longest sequence the key just before the query's
     chunk is made enormous along one query's direction (it must not be seen: it would take the whole softmax), and
