@@ -361,7 +361,7 @@ def run_workload(args):
     """BASELINE.json's fourth (GPT-2 medium: 16 prompts of 1 to 900 tokens, one prompt step, decoded to
     1,024 at temperature 1.0) or fifth (GPT-2 XL: 64 prompts of 128 tokens, greedy to a full cache)
     workload through ``LLM.generate``, prompt step and decoding timed apart as the reference's own
-    report does (src/LLM.cpp:687-738).  One JSON line; not the contract's bench record."""
+    report does (src/LLM.cpp:687-738).  One JSON line; not the record that the default run prints."""
     import numpy as np
     import torch
     name = args.config
